@@ -1,6 +1,7 @@
 from .model_config import ConfigError, Qwen3Config, read_config_json, FULL_ATTENTION, SLIDING_ATTENTION
 from .lokinex_config import LokinexConfig
 from .tabedra_config import TabedraConfig
+from .kupelix_config import KupelixConfig
 from .engine_config import EngineConfig
 from .registry import (Architecture, register_architecture, unregister_architecture, registered_architectures,
                        resolve_architecture, load_model_config)

@@ -1,0 +1,378 @@
+// Mixers that keep a matrix of state per head instead of a cache of keys, for both engines:
+//   * state_recurrence: per (sequence, head) a [rows, columns] float32 state walked token by token, in two forms:
+//       gated write   S = diag(g) S + w v^T,                                    o = S^T q      (HGRN2: g = f, w = 1 - f)
+//       delta rule    S = diag(g) S;  u = beta (v - S^T k);  S = S + k u^T;     o = S^T q      (decay per key channel)
+//   * hgrn2_prep: q = silu(.), forget gate with a lower bound, both laid out in padded rows;
+//   * delta_prep: short convolution over time + silu on q, k, v; unit-length q and k; decay and write strength;
+//   * conv_tail_update: a request's last taps - 1 projected rows after the step;
+//   * head_norm_gate: every head's read-out divided by its root mean square, times a weight and a sigmoid gate;
+//   * activation: elementwise xIELU / tanh-GELU;  scale_rows: float32 rows times one number.
+// Gates, decays, norms and the state are float32 whatever the engine's element type.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+__device__ __forceinline__ void store_any(void* p, int dt, size_t i, float v) {
+    if (dt == RS_F32) reinterpret_cast<float*>(p)[i] = v;
+    else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// ------------------------------------------------------------------------------------------------ the recurrence
+// A column of a head's state belongs to 8 neighbouring lanes; each keeps RPT neighbouring rows of it in registers, so
+// a head has up to 8 * RPT rows.  A warp walks 4 columns, a CTA 32.  Sums over rows are three shuffles inside the 8
+// lanes: no shared memory and no barrier in the token loop, and an order of additions that depends on nothing but
+// the head's shape.  In a request's slot a head's state is stored column by column ([column][padded rows]), so the
+// loads and stores at both ends of a step are whole 16-byte runs.
+constexpr int ROW_LANES = 8;
+constexpr int COLS_PER_CTA = 32;
+
+struct RecurrenceParams {
+    const float* q; long q_stride;          // [T, q heads * rows_pad]
+    const float* k; long k_stride;          // delta rule: keys [T, q heads * rows_pad]; gated write: w [T, heads * rows_pad]
+    const float* g; long g_stride;          // [T, heads * rows_pad] decay of every row
+    const float* beta; long beta_stride;    // [T, heads] (delta rule)
+    const float* v; long v_stride;          // [T, heads * columns]
+    float* out; long out_stride;            // [T, heads * columns]
+    float* state; long state_stride;        // [slots, heads * columns * rows_pad]
+    const int* q_start; const int* slots;
+    int heads, group, columns;              // group: state heads per q/k head (delta rule)
+};
+
+__device__ __forceinline__ float sum_row_lanes(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+template <int RPT>
+__device__ __forceinline__ void load_rows(const float* p, float* r) {
+#pragma unroll
+    for (int m = 0; m < RPT; m += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p + m);
+        r[m] = a.x; r[m + 1] = a.y; r[m + 2] = a.z; r[m + 3] = a.w;
+    }
+}
+
+template <int RPT, bool DELTA>
+__global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams p) {
+    constexpr int RP = RPT * ROW_LANES;                  // padded rows of a head
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rl = lane & 7, cl = lane >> 3;
+    const int s = blockIdx.x / p.heads, h = blockIdx.x % p.heads;
+    const int j = blockIdx.y * COLS_PER_CTA + warp * 4 + cl;
+    const bool live = j < p.columns;
+    const int jc = live ? j : p.columns - 1;              // lanes beyond the last column walk it too and store nothing
+    const int t0 = p.q_start[s], t1 = p.q_start[s + 1];
+    float* sp = p.state + (size_t)p.slots[s] * p.state_stride + ((size_t)h * p.columns + jc) * RP + rl * RPT;
+    float S[RPT];
+    load_rows<RPT>(sp, S);
+    const size_t qk_off = (size_t)(DELTA ? h / p.group : h) * RP + rl * RPT;
+    const size_t k_off = DELTA ? qk_off : (size_t)h * RP + rl * RPT;
+    const size_t g_off = (size_t)h * RP + rl * RPT;
+    float qn[RPT], kn[RPT], gn[RPT];
+    float vn = 0.f, bn = 0.f;
+    if (t0 < t1) {
+        load_rows<RPT>(p.q + (size_t)t0 * p.q_stride + qk_off, qn);
+        load_rows<RPT>(p.k + (size_t)t0 * p.k_stride + k_off, kn);
+        load_rows<RPT>(p.g + (size_t)t0 * p.g_stride + g_off, gn);
+        vn = p.v[(size_t)t0 * p.v_stride + (size_t)h * p.columns + jc];
+        if (DELTA) bn = p.beta[(size_t)t0 * p.beta_stride + h];
+    }
+    for (int t = t0; t < t1; ++t) {
+        float qc[RPT], kc[RPT], gc[RPT];
+#pragma unroll
+        for (int m = 0; m < RPT; ++m) { qc[m] = qn[m]; kc[m] = kn[m]; gc[m] = gn[m]; }
+        const float vc = vn, bc = bn;
+        if (t + 1 < t1) {                                  // the next token's rows are on their way while this one is worked
+            load_rows<RPT>(p.q + (size_t)(t + 1) * p.q_stride + qk_off, qn);
+            load_rows<RPT>(p.k + (size_t)(t + 1) * p.k_stride + k_off, kn);
+            load_rows<RPT>(p.g + (size_t)(t + 1) * p.g_stride + g_off, gn);
+            vn = p.v[(size_t)(t + 1) * p.v_stride + (size_t)h * p.columns + jc];
+            if (DELTA) bn = p.beta[(size_t)(t + 1) * p.beta_stride + h];
+        }
+        float acc = 0.f;
+        if (DELTA) {
+            float r = 0.f;
+#pragma unroll
+            for (int m = 0; m < RPT; ++m) { S[m] *= gc[m]; r = fmaf(S[m], kc[m], r); }
+            r = sum_row_lanes(r);
+            const float u = bc * (vc - r);
+#pragma unroll
+            for (int m = 0; m < RPT; ++m) { S[m] = fmaf(kc[m], u, S[m]); acc = fmaf(S[m], qc[m], acc); }
+        } else {
+#pragma unroll
+            for (int m = 0; m < RPT; ++m) { S[m] = fmaf(gc[m], S[m], kc[m] * vc); acc = fmaf(S[m], qc[m], acc); }
+        }
+        acc = sum_row_lanes(acc);
+        if (rl == 0 && live) p.out[(size_t)t * p.out_stride + (size_t)h * p.columns + j] = acc;
+    }
+    if (live) {
+#pragma unroll
+        for (int m = 0; m < RPT; m += 4) *reinterpret_cast<float4*>(sp + m) = make_float4(S[m], S[m + 1], S[m + 2], S[m + 3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ HGRN2: gates
+// proj [T, q (heads * dim) | f (heads * dim) | ...] float32: q = silu(.), f = l + (1 - l) sigmoid(. + bias);
+// rows padded to rows_pad with zeros (a padded row of the state stays zero whatever it is multiplied by).
+__global__ void hgrn2_prep_kernel(const float* proj, long proj_stride, const void* f_bias, int fb_dt, const void* lower, int lo_dt,
+                                  float* q, float* g, float* w, int heads, int dim, int rows_pad, long n) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int i = (int)(idx % rows_pad);
+    const int h = (int)((idx / rows_pad) % heads);
+    const long t = idx / ((long)rows_pad * heads);
+    float qv = 0.f, gv = 0.f, wv = 0.f;
+    if (i < dim) {
+        const int c = h * dim + i;
+        const float* row = proj + t * proj_stride;
+        qv = silu_f(row[c]);
+        const float lo = load_any(lower, lo_dt, c);
+        const float pre = row[heads * dim + c] + (f_bias ? load_any(f_bias, fb_dt, c) : 0.f);
+        gv = lo + (1.0f - lo) * sigmoid_f(pre);
+        wv = 1.0f - gv;
+    }
+    q[idx] = qv; g[idx] = gv; w[idx] = wv;
+}
+
+// ------------------------------------------------------------------------------------------------ delta rule: inputs
+constexpr int MAX_PER_LANE = 8;          // heads of up to 256 channels
+
+struct DeltaPrepParams {
+    const float* proj; long proj_stride;      // [T, q (qk heads * dim) | k (qk heads * dim) | v (heads * vdim) | beta (heads) | ...]
+    const void* conv; int conv_dt;            // [taps, C] tap-major, C = the q, k and v channels; null with taps <= 1... or 0
+    const float* tail; long tail_stride;      // [slots, (taps - 1) * C]
+    const float* step; long step_stride;      // [T, heads * dim]: what the decay's softplus reads, before its bias
+    const void* dt_bias; int dtb_dt;          // [heads * dim]
+    const void* a_log; int al_dt;             // [heads]
+    float* q; float* k; float* g;             // [T, qk heads * rows_pad] x 2, [T, heads * rows_pad]
+    float* v; float* beta;                    // [T, heads * vdim], [T, heads]
+    const int* seq_of_token; const int* q_start; const int* slots;
+    int C, taps, qk_heads, heads, dim, vdim, rows_pad, beta_off, n_tokens;
+    float unit_eps, q_scale;
+};
+
+// A warp per (token, item); items: the q heads, the k heads, the v heads, then one per head for decay and strength.
+__global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepParams p) {
+    const int lane = threadIdx.x & 31;
+    const int items = 2 * p.qk_heads + 2 * p.heads;
+    const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long)p.n_tokens * items) return;
+    const int t = (int)(wid / items), item = (int)(wid % items);
+    if (item >= 2 * p.qk_heads + p.heads) {               // decay of every key channel, and the write strength
+        const int h = item - 2 * p.qk_heads - p.heads;
+        const float rate = expf(load_any(p.a_log, p.al_dt, h));
+        for (int i = lane; i < p.rows_pad; i += 32) {
+            float gv = 0.f;
+            if (i < p.dim) {
+                const int c = h * p.dim + i;
+                gv = expf(-rate * softplus_f(p.step[(size_t)t * p.step_stride + c] + load_any(p.dt_bias, p.dtb_dt, c)));
+            }
+            p.g[((size_t)t * p.heads + h) * p.rows_pad + i] = gv;
+        }
+        if (lane == 0) p.beta[(size_t)t * p.heads + h] = sigmoid_f(p.proj[(size_t)t * p.proj_stride + p.beta_off + h]);
+        return;
+    }
+    int kind, base, width, head;
+    if (item < p.qk_heads) { kind = 0; head = item; base = head * p.dim; width = p.dim; }
+    else if (item < 2 * p.qk_heads) { kind = 1; head = item - p.qk_heads; base = (p.qk_heads + head) * p.dim; width = p.dim; }
+    else { kind = 2; head = item - 2 * p.qk_heads; base = 2 * p.qk_heads * p.dim + head * p.vdim; width = p.vdim; }
+    const int s = p.seq_of_token[t];
+    const int t0 = p.q_start[s];
+    const float* tail = p.tail ? p.tail + (size_t)p.slots[s] * p.tail_stride : nullptr;
+    float acc[MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int m = 0; m < MAX_PER_LANE; ++m) {
+        const int d = lane + 32 * m;
+        acc[m] = 0.f;
+        if (d < width) {
+            const int c = base + d;
+            float a;
+            if (p.taps >= 1 && p.conv) {
+                a = 0.f;
+                for (int jt = 0; jt < p.taps; ++jt) {
+                    const int back = p.taps - 1 - jt;                  // how many tokens before t this tap reads
+                    float x;
+                    if (t - back >= t0) x = p.proj[(size_t)(t - back) * p.proj_stride + c];
+                    else x = tail[(size_t)(p.taps - 1 - (t0 - (t - back))) * p.C + c];
+                    a = fmaf(load_any(p.conv, p.conv_dt, (size_t)jt * p.C + c), x, a);
+                }
+            } else {
+                a = p.proj[(size_t)t * p.proj_stride + c];
+            }
+            a = silu_f(a);
+            acc[m] = a;
+            ss = fmaf(a, a, ss);
+        }
+    }
+    if (kind == 2) {
+#pragma unroll
+        for (int m = 0; m < MAX_PER_LANE; ++m) {
+            const int d = lane + 32 * m;
+            if (d < width) p.v[((size_t)t * p.heads + head) * p.vdim + d] = acc[m];
+        }
+        return;
+    }
+    ss = warp_sum(ss);
+    const float r = (kind == 0 ? p.q_scale : 1.0f) / sqrtf(ss + p.unit_eps);
+    float* dst = (kind == 0 ? p.q : p.k) + ((size_t)t * p.qk_heads + head) * p.rows_pad;
+#pragma unroll
+    for (int m = 0; m < MAX_PER_LANE; ++m) {
+        const int d = lane + 32 * m;
+        if (d < p.rows_pad) dst[d] = d < width ? acc[m] * r : 0.f;
+    }
+}
+
+// After the step: a request's tail holds the last taps - 1 projected rows it has seen.  One thread per (sequence, channel)
+// walks the tail from its oldest row on: what it reads lies at or after what it writes.
+__global__ void conv_tail_update_kernel(const float* proj, long proj_stride, float* tail, long tail_stride, const int* q_start,
+                                        const int* slots, int C, int taps, int n_seqs) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_seqs * C) return;
+    const int s = (int)(idx / C), c = (int)(idx % C);
+    const int t0 = q_start[s], t1 = q_start[s + 1], n = t1 - t0, keep = taps - 1;
+    float* row = tail + (size_t)slots[s] * tail_stride;
+    for (int e = 0; e < keep; ++e) {
+        const int t = t1 - keep + e;
+        row[(size_t)e * C + c] = t >= t0 ? proj[(size_t)t * proj_stride + c] : row[(size_t)(e + n) * C + c];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ read-out
+// A warp per (token, head): o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) (weight and gate optional).
+__global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* o, long o_stride, const void* weight, int w_dt, const float* gate,
+                                                            long gate_stride, void* out, int out_dt, long out_stride, int heads, int vdim,
+                                                            float eps, int n_tokens) {
+    const int lane = threadIdx.x & 31;
+    const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long)n_tokens * heads) return;
+    const int t = (int)(wid / heads), h = (int)(wid % heads);
+    const float* row = o + (size_t)t * o_stride + (size_t)h * vdim;
+    float ss = 0.f;
+    for (int d = lane; d < vdim; d += 32) ss = fmaf(row[d], row[d], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int d = lane; d < vdim; d += 32) {
+        float y = row[d] * r;
+        if (weight) y *= load_any(weight, w_dt, d);
+        if (gate) y *= sigmoid_f(gate[(size_t)t * gate_stride + (size_t)h * vdim + d]);
+        store_any(out, out_dt, (size_t)t * out_stride + (size_t)h * vdim + d, y);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ activations
+enum Activation : int { ACT_XIELU = 0, ACT_GELU_TANH = 1 };
+
+// xIELU with two learned numbers (p, q): z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+template <typename T>
+__global__ void activation_kernel(const T* x, long x_stride, T* out, long out_stride, int width, long n, int kind, const void* pq, int pq_dt) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const long t = idx / width; const int c = (int)(idx % width);
+    const float z = to_f32<T>(x[t * x_stride + c]);
+    float y;
+    if (kind == ACT_XIELU) {
+        const float ap = softplus_f(load_any(pq, pq_dt, 0)), an = 0.5f + softplus_f(load_any(pq, pq_dt, 1));
+        y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    } else {
+        y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    }
+    out[t * out_stride + c] = from_f32<T>(y);
+}
+
+__global__ void scale_rows_kernel(float* x, long stride, int width, long n, float scale) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    x[(idx / width) * stride + idx % width] *= scale;
+}
+
+}  // namespace
+
+// ==================================================================================================== entry points
+RS_EXPORT int rs_state_recurrence_rows_pad(int rows) {
+    for (int rpt = 4; rpt <= 32; rpt *= 2) if (rows <= rpt * ROW_LANES) return rpt * ROW_LANES;
+    return 0;
+}
+
+RS_EXPORT int rs_state_recurrence(const float* q, long q_stride, const float* k, long k_stride, const float* g, long g_stride,
+                                  const float* beta, long beta_stride, const float* v, long v_stride, float* out, long out_stride,
+                                  float* state, long state_stride, const int* q_start, const int* slots, int n_seqs, int heads,
+                                  int group, int rows_pad, int columns, int delta, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    RecurrenceParams p{q, q_stride, k, k_stride, g, g_stride, beta, beta_stride, v, v_stride, out, out_stride, state, state_stride,
+                       q_start, slots, heads, group < 1 ? 1 : group, columns};
+    const dim3 grid(n_seqs * heads, (columns + COLS_PER_CTA - 1) / COLS_PER_CTA);
+#define RS_REC(RPT)                                                                                   \
+    case RPT * ROW_LANES:                                                                             \
+        if (delta) state_recurrence_kernel<RPT, true><<<grid, 256, 0, stream>>>(p);                   \
+        else state_recurrence_kernel<RPT, false><<<grid, 256, 0, stream>>>(p);                        \
+        break;
+    switch (rows_pad) {
+        RS_REC(4) RS_REC(8) RS_REC(16) RS_REC(32)
+        default: return (int)cudaErrorInvalidValue;
+    }
+#undef RS_REC
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_hgrn2_prep(const float* proj, long proj_stride, const void* f_bias, int fb_dt, const void* lower, int lo_dt, float* q,
+                            float* g, float* w, int heads, int dim, int rows_pad, int n_tokens, cudaStream_t stream) {
+    const long n = (long)n_tokens * heads * rows_pad;
+    if (n <= 0) return 0;
+    hgrn2_prep_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(proj, proj_stride, f_bias, fb_dt, lower, lo_dt, q, g, w, heads,
+                                                                      dim, rows_pad, n);
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_delta_prep(const float* proj, long proj_stride, const void* conv, int conv_dt, float* tail, long tail_stride,
+                            const float* step, long step_stride, const void* dt_bias, int dtb_dt, const void* a_log, int al_dt,
+                            float* q, float* k, float* g, float* v, float* beta, const int* seq_of_token, const int* q_start,
+                            const int* slots, int taps, int qk_heads, int heads, int dim, int vdim, int rows_pad, int beta_off,
+                            float unit_eps, float q_scale, int n_tokens, int n_seqs, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dim > 32 * MAX_PER_LANE || vdim > 32 * MAX_PER_LANE || rows_pad > 32 * MAX_PER_LANE) return (int)cudaErrorInvalidValue;
+    DeltaPrepParams p{proj, proj_stride, conv, conv_dt, tail, tail_stride, step, step_stride, dt_bias, dtb_dt, a_log, al_dt,
+                      q, k, g, v, beta, seq_of_token, q_start, slots, 2 * qk_heads * dim + heads * vdim, taps, qk_heads, heads,
+                      dim, vdim, rows_pad, beta_off, n_tokens, unit_eps, q_scale};
+    const long warps = (long)n_tokens * (2 * qk_heads + 2 * heads);
+    delta_prep_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(p);
+    int rc = rs_launch_result();
+    if (rc || taps <= 1 || !conv) return rc;
+    const long n = (long)n_seqs * p.C;
+    conv_tail_update_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(proj, proj_stride, tail, tail_stride, q_start, slots,
+                                                                            p.C, taps, n_seqs);
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_head_norm_gate(const float* o, long o_stride, const void* weight, int w_dt, const float* gate, long gate_stride,
+                                void* out, int out_dt, long out_stride, int heads, int vdim, float eps, int n_tokens,
+                                cudaStream_t stream) {
+    const long warps = (long)n_tokens * heads;
+    if (warps <= 0) return 0;
+    head_norm_gate_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(o, o_stride, weight, w_dt, gate, gate_stride, out, out_dt,
+                                                                          out_stride, heads, vdim, eps, n_tokens);
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_activation(const void* x, long x_stride, void* out, long out_stride, int dt, int width, int n_rows, int kind,
+                            const void* pq, int pq_dt, cudaStream_t stream) {
+    const long n = (long)n_rows * width;
+    if (n <= 0) return 0;
+    if (kind == ACT_XIELU && !pq) return (int)cudaErrorInvalidValue;
+    RS_DISPATCH_DTYPE(dt, T, (activation_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<T*>(out), out_stride, width, n, kind, pq, pq_dt)));
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_scale_rows(float* x, long stride, int width, int n_rows, float scale, cudaStream_t stream) {
+    const long n = (long)n_rows * width;
+    if (n <= 0) return 0;
+    scale_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, stride, width, n, scale);
+    return rs_launch_result();
+}

@@ -1521,3 +1521,228 @@ def sigmoid_gate(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tenso
         raise KernelError("sigmoid_gate: a [T, heads * head_pad], gate and out [T, heads * dv], one element type")
     _check(streamlib().rs_sigmoid_gate(_ptr(a), a.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(out),
                                        out.stride(0), dtype_code(a), n_heads, dv, head_pad, n_tokens, _stream()), "sigmoid_gate")
+
+
+# ----------------------------------------------------------------------------- state-matrix mixers, talking-heads attention
+_mixerslib = None
+
+ACT_XIELU, ACT_GELU_TANH = 0, 1
+ACTIVATIONS = {"xielu": ACT_XIELU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def mixerslib():
+    global _mixerslib
+    if _mixerslib is None:
+        lib = load_library("mixers")
+        lib.rs_state_recurrence_rows_pad.argtypes = [c_int]
+        lib.rs_state_recurrence.argtypes = [c_void_p, c_long] * 7 + [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                                     c_void_p]
+        lib.rs_hgrn2_prep.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_void_p]
+        lib.rs_delta_prep.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_void_p,
+                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]
+        lib.rs_head_norm_gate.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_int,
+                                          c_float, c_int, c_void_p]
+        lib.rs_activation.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rs_scale_rows.argtypes = [c_void_p, c_long, c_int, c_int, c_float, c_void_p]
+        lib.rs_talking_attention_q_per_cta.argtypes = [c_int, c_int, c_int]
+        lib.rs_talking_attention_prep.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int,
+                                                  c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int,
+                                                  c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                  c_void_p, c_void_p]
+        lib.rs_talking_attention.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_long, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+        _mixerslib = lib
+    return _mixerslib
+
+
+def _f32_rows(who: str, **ts) -> None:
+    for name, t in ts.items():
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"{who}: {name} must be float32 [rows, width] on the device with unit stride along its last axis")
+
+
+def state_rows_pad(rows: int) -> int:
+    """Rows a head of the state-matrix recurrence is padded to (its per-row inputs are laid out with this pitch)."""
+    if rows <= 32:
+        return 32
+    n = 32
+    while n < rows:
+        n *= 2
+    if n > 256:
+        raise KernelError(f"state recurrence: {rows} rows per head (up to 256 are supported)")
+    return n
+
+
+def state_recurrence(q: torch.Tensor, k: torch.Tensor, g: torch.Tensor, beta: Optional[torch.Tensor], v: torch.Tensor,
+                     out: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, heads: int,
+                     group: int, rows_pad: int, columns: int, delta: bool) -> None:
+    """Per (sequence, head) a float32 state S [rows, columns] walked over the step's tokens (csrc/state_mixers.cu).
+
+    ``delta`` False: S = diag(g) S + k v^T, out = S^T q, with q, k, g [T, heads * rows_pad].
+    ``delta`` True:  S = diag(g) S; u = beta (v - S^T k); S += k u^T; out = S^T q, with q and k [T, (heads / group) *
+    rows_pad] (state head h reads q/k head h // group), g [T, heads * rows_pad], beta [T, heads].
+    v, out [T, heads * columns]; state [slots, >= heads * columns * rows_pad], each head stored column by column."""
+    _cuda(q, k, g, beta, v, out, state, q_start, slots)
+    _f32_rows("state_recurrence", q=q, k=k, g=g, beta=beta, v=v, out=out, state=state)
+    _i32("state_recurrence", q_start, slots)
+    if delta and beta is None:
+        raise KernelError("state_recurrence: the delta rule needs a write strength per head")
+    qk_heads = heads // group if delta else heads
+    if q.shape[1] < qk_heads * rows_pad or k.shape[1] < qk_heads * rows_pad or g.shape[1] < heads * rows_pad \
+            or v.shape[1] < heads * columns or out.shape[1] < heads * columns or state.shape[1] < heads * columns * rows_pad:
+        raise KernelError("state_recurrence: an operand is narrower than heads x rows / columns ask for")
+    for name, t in (("q", q), ("k", k), ("g", g), ("state", state)):
+        if t.stride(0) % 4 or t.data_ptr() % 16:
+            raise KernelError(f"state_recurrence: {name} must start on 16 bytes with a row pitch that is a multiple of 4")
+    _check(mixerslib().rs_state_recurrence(
+        _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(g), g.stride(0), _ptr(beta), 0 if beta is None else beta.stride(0),
+        _ptr(v), v.stride(0), _ptr(out), out.stride(0), _ptr(state), state.stride(0), _ptr(q_start), _ptr(slots), n_seqs, heads,
+        group, rows_pad, columns, 1 if delta else 0, _stream()), "state_recurrence")
+
+
+def hgrn2_prep(proj: torch.Tensor, f_bias: Optional[torch.Tensor], lower: torch.Tensor, q: torch.Tensor, g: torch.Tensor,
+               w: torch.Tensor, heads: int, dim: int, rows_pad: int, n_tokens: int) -> None:
+    """From proj [T, q | f | ...] (float32): q = silu(.), g = lower + (1 - lower) sigmoid(f + bias), w = 1 - g, each
+    [T, heads * rows_pad] contiguous, padding zero."""
+    _cuda(proj, f_bias, lower, q, g, w)
+    _f32_rows("hgrn2_prep", proj=proj, q=q, g=g, w=w)
+    if proj.shape[1] < 2 * heads * dim or any(t.shape[1] != heads * rows_pad or not t.is_contiguous() for t in (q, g, w)) \
+            or lower.numel() != heads * dim or (f_bias is not None and f_bias.numel() != heads * dim):
+        raise KernelError("hgrn2_prep: shapes do not fit heads x dim")
+    _check(mixerslib().rs_hgrn2_prep(_ptr(proj), proj.stride(0), _ptr(f_bias), _any_code(f_bias), _ptr(lower), dtype_code(lower),
+                                     _ptr(q), _ptr(g), _ptr(w), heads, dim, rows_pad, n_tokens, _stream()), "hgrn2_prep")
+
+
+def delta_prep(proj: torch.Tensor, conv: Optional[torch.Tensor], tail: Optional[torch.Tensor], step: torch.Tensor,
+               dt_bias: torch.Tensor, a_log: torch.Tensor, q: torch.Tensor, k: torch.Tensor, g: torch.Tensor, v: torch.Tensor,
+               beta: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, qk_heads: int,
+               heads: int, dim: int, vdim: int, rows_pad: int, beta_off: int, unit_eps: float, q_scale: float, n_tokens: int,
+               n_seqs: int) -> None:
+    """Inputs of the delta-rule recurrence from proj [T, q | k | v | ... beta at ``beta_off``] (float32): a causal
+    convolution over time per channel of q, k, v (``conv`` [taps, C] tap-major; ``tail`` [slots, >= (taps - 1) * C] holds
+    every request's last projected rows and is updated), silu, q and k heads to unit length (q times ``q_scale``), the
+    decay g = exp(-exp(a_log[h]) softplus(step + dt_bias)) per head and key channel, beta = sigmoid(.)."""
+    _cuda(proj, conv, tail, step, dt_bias, a_log, q, k, g, v, beta, seq_of_token, q_start, slots)
+    _f32_rows("delta_prep", proj=proj, step=step, q=q, k=k, g=g, v=v, beta=beta, tail=tail)
+    _i32("delta_prep", seq_of_token, q_start, slots)
+    C = 2 * qk_heads * dim + heads * vdim
+    taps = 0 if conv is None else conv.shape[0]
+    if conv is not None and (tuple(conv.shape) != (taps, C) or not conv.is_contiguous()):
+        raise KernelError(f"delta_prep: the convolution's weight must be contiguous [taps, {C}]")
+    if taps > 1 and (tail is None or tail.shape[1] < (taps - 1) * C):
+        raise KernelError("delta_prep: tail must hold (taps - 1) * channels values per slot")
+    if proj.shape[1] < max(C, beta_off + heads) or step.shape[1] < heads * dim or dt_bias.numel() != heads * dim \
+            or a_log.numel() != heads or not all(t.is_contiguous() for t in (q, k, g, v, beta)) \
+            or q.shape[1] != qk_heads * rows_pad or k.shape[1] != qk_heads * rows_pad or g.shape[1] != heads * rows_pad \
+            or v.shape[1] != heads * vdim or beta.shape[1] != heads:
+        raise KernelError("delta_prep: shapes do not fit the head counts and sizes")
+    _check(mixerslib().rs_delta_prep(
+        _ptr(proj), proj.stride(0), _ptr(conv), _any_code(conv), _ptr(tail), 0 if tail is None else tail.stride(0), _ptr(step),
+        step.stride(0), _ptr(dt_bias), dtype_code(dt_bias), _ptr(a_log), dtype_code(a_log), _ptr(q), _ptr(k), _ptr(g), _ptr(v),
+        _ptr(beta), _ptr(seq_of_token), _ptr(q_start), _ptr(slots), taps, qk_heads, heads, dim, vdim, rows_pad, beta_off,
+        float(unit_eps), float(q_scale), n_tokens, n_seqs, _stream()), "delta_prep", 2 if taps > 1 else 1)
+
+
+def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor, heads: int,
+                   vdim: int, eps: float, n_tokens: int) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * sigmoid(gate[t, h, :]); o and gate float32."""
+    _cuda(o, weight, gate, out)
+    _f32_rows("head_norm_gate", o=o, gate=gate)
+    _rows_contiguous(out, "head_norm_gate out")
+    if o.shape[1] < heads * vdim or out.shape[1] < heads * vdim or (gate is not None and gate.shape[1] < heads * vdim) \
+            or (weight is not None and weight.numel() != vdim):
+        raise KernelError("head_norm_gate: shapes do not fit heads x vdim")
+    _check(mixerslib().rs_head_norm_gate(_ptr(o), o.stride(0), _ptr(weight), _any_code(weight), _ptr(gate),
+                                         0 if gate is None else gate.stride(0), _ptr(out), dtype_code(out), out.stride(0), heads,
+                                         vdim, float(eps), n_tokens, _stream()), "head_norm_gate")
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, n_rows: int, kind: str, params: Optional[torch.Tensor] = None) -> None:
+    """Elementwise activation of the first n_rows rows (float32 arithmetic): "xielu" with ``params`` = (p, q):
+    z > 0: softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;  "gelu_tanh"."""
+    _cuda(x, out, params)
+    _rows_contiguous(x, "activation x")
+    _rows_contiguous(out, "activation out")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind '{kind}' (known: {', '.join(sorted(ACTIVATIONS))})")
+    if x.dtype != out.dtype or x.shape[1] != out.shape[1] or n_rows > min(x.shape[0], out.shape[0]):
+        raise KernelError("activation: x and out must share element type and width")
+    if kind == "xielu" and (params is None or params.numel() != 2):
+        raise KernelError("activation: xielu takes two numbers")
+    _check(mixerslib().rs_activation(_ptr(x), x.stride(0), _ptr(out), out.stride(0), dtype_code(x), x.shape[1], n_rows,
+                                     ACTIVATIONS[kind], _ptr(params), _any_code(params), _stream()), "activation")
+
+
+def scale_rows(x: torch.Tensor, n_rows: int, scale: float) -> None:
+    """x[:n_rows] *= scale for float32 rows."""
+    _cuda(x)
+    _f32_rows("scale_rows", x=x)
+    _check(mixerslib().rs_scale_rows(_ptr(x), x.stride(0), x.shape[1], n_rows, float(scale), _stream()), "scale_rows")
+
+
+def talking_attention_q_per_cta(n_heads: int, dk: int, dv: int) -> int:
+    n = int(mixerslib().rs_talking_attention_q_per_cta(n_heads, dk, dv))
+    if n < 1:
+        raise KernelError(f"talking attention: {n_heads} heads of {dk}/{dv} do not fit a CTA's shared memory")
+    return n
+
+
+def talking_attention_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
+                           k_norm: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], n_rot: int,
+                           q_out: torch.Tensor, gate_out: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
+                           page_size: int, positions: torch.Tensor, seq_of_token: torch.Tensor, n_heads: int, n_kv: int, dk: int,
+                           dv: int, n_tokens: int, write_kv: bool, status: torch.Tensor) -> None:
+    """proj [T, q | k | v | gate] float32 (+ bias): RMS norm of q and k heads (weights [dk], None: none), rotation of
+    the first ``n_rot`` coordinates in neighbouring pairs by ``cos_sin`` [positions, cos | sin], q to ``q_out`` float32
+    [T, heads * dk], k and v into ``cache`` [pages, 2, n_kv, page_size, head_pad] (padding zero), sigmoid of the gates
+    to ``gate_out`` float32 [T, heads]."""
+    _cuda(proj, bias, q_norm, k_norm, cos_sin, q_out, gate_out, cache, block_table, positions, seq_of_token, status)
+    _f32_rows("talking_attention_prep", proj=proj, q_out=q_out, gate_out=gate_out, cos_sin=cos_sin)
+    _i32("talking_attention_prep", block_table, positions, seq_of_token)
+    hdp = cache.shape[-1]
+    width = n_heads * dk + n_kv * (dk + dv)
+    if proj.shape[1] < width + (n_heads if gate_out is not None else 0) or q_out.shape[1] < n_heads * dk \
+            or (bias is not None and bias.numel() != width) or not cache.is_contiguous() \
+            or tuple(cache.shape[1:]) != (2, n_kv, page_size, hdp) or hdp < max(dk, dv) \
+            or (gate_out is not None and (gate_out.shape[1] != n_heads or not gate_out.is_contiguous())):
+        raise KernelError("talking_attention_prep: shapes do not fit the head counts and sizes")
+    if (q_norm is None) != (k_norm is None) or (q_norm is not None and (q_norm.numel() != dk or k_norm.numel() != dk
+                                                                        or q_norm.dtype != k_norm.dtype)):
+        raise KernelError("talking_attention_prep: q and k norm weights come together, [dk] each, one element type")
+    if n_rot and (cos_sin is None or cos_sin.shape[1] != n_rot or not cos_sin.is_contiguous()):
+        raise KernelError("talking_attention_prep: the rotation table must be contiguous [positions, n_rot]")
+    _check(mixerslib().rs_talking_attention_prep(
+        _ptr(proj), proj.stride(0), _ptr(bias), _any_code(bias), _ptr(q_norm), _ptr(k_norm), _any_code(q_norm), float(eps),
+        _ptr(cos_sin), n_rot if cos_sin is not None else 0, 0 if cos_sin is None else cos_sin.shape[0], _ptr(q_out),
+        q_out.stride(0), _ptr(gate_out), _ptr(cache), dtype_code(cache), cache.stride(0), cache.shape[0], page_size, hdp,
+        _ptr(block_table), block_table.stride(0), _ptr(positions), positions.stride(0), _ptr(seq_of_token), n_heads, n_kv, dk, dv,
+        n_tokens, 1 if write_kv else 0, _ptr(status), _stream()), "talking_attention_prep")
+
+
+def talking_attention(q: torch.Tensor, gate: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
+                      page_size: int, q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int,
+                      talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], out: torch.Tensor, n_heads: int, n_kv: int,
+                      dk: int, dv: int, window: int, q_per_cta: int, scale: float, status: torch.Tensor) -> None:
+    """Causal attention of the step's queries over the paged cache with scores mixed across heads (``talk`` float32
+    [heads, heads]: mixed[h] = sum_g talk[h, g] raw[g]) before a softmax whose denominator also holds exp(sink[h]);
+    every head's output times ``gate`` [T, heads].  ``work``: (sequence, first query) per tile of ``q_per_cta`` queries."""
+    _cuda(q, gate, cache, block_table, q_start, kv_len, work, talk, sink, out, status)
+    _f32_rows("talking_attention", q=q, gate=gate)
+    _rows_contiguous(out, "talking_attention out")
+    _i32("talking_attention", block_table, q_start, kv_len, work)
+    for name, t, n in (("talk", talk, n_heads * n_heads), ("sink", sink, n_heads)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError(f"talking_attention: {name} must be contiguous float32 with {n} values")
+    if q.shape[1] < n_heads * dk or out.shape[1] < n_heads * dv or work.numel() < 2 * n_work or not cache.is_contiguous() \
+            or (gate is not None and (gate.shape[1] != n_heads or not gate.is_contiguous())):
+        raise KernelError("talking_attention: shapes do not fit the head counts and sizes")
+    _check(mixerslib().rs_talking_attention(
+        _ptr(q), q.stride(0), _ptr(gate), _ptr(cache), dtype_code(cache), cache.stride(0), cache.shape[0], page_size,
+        cache.shape[-1], _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, _ptr(talk),
+        _ptr(sink), _ptr(out), dtype_code(out), out.stride(0), n_heads, n_kv, dk, dv, window, q_per_cta, float(scale),
+        _ptr(status), _stream()), "talking_attention")

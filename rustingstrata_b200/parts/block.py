@@ -43,6 +43,35 @@ class PreNormBlock(Block):
         ctx.may_owe = False
 
 
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    """One norm whose output both sublayers read: with h = norm(x), x += mixer(h) + feed_forward(h).
+
+    params: hidden.  Made of: norm, mixer, and optionally feed_forward (a position encoding for the mixer, if the layer
+    lists one).  Both sublayers add their output into the float32 stream, the mixer first."""
+    roles = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional = ("feed_forward",)
+
+    def __init__(self, spec, runtime, parts):
+        super().__init__(spec, runtime, parts)
+        self.norm, self.mixer, self.feed_forward = parts["norm"], parts["mixer"], parts.get("feed_forward")
+        self.hidden = int(spec.params["hidden"])
+        runtime.scratch("normed", runtime.max_batch_tokens, self.hidden)
+
+    @property
+    def first_reader_takes_owed(self):
+        return getattr(self.norm, "takes_owed", False)
+
+    def forward(self, residual, ctx, call):
+        h = self.runtime.get_scratch("normed")[:, : self.hidden]
+        self.norm_of_stream(self.norm, residual, h, ctx)
+        # neither sublayer may leave a sum owed to the stream: the other one adds into it right after
+        ctx.may_owe = False
+        self.mixer.forward(h, residual, ctx, call.mixers["mixer"])
+        if self.feed_forward is not None:
+            self.feed_forward.forward(h, residual, ctx)
+
+
 @register_part("block", "sandwich_norm")
 class SandwichNormBlock(Block):
     """A layer whose sublayers are normed on both sides: x += post(mixer(conv(pre(x)))), x += post'(ff(pre'(x))).
@@ -105,7 +134,8 @@ class StreamReentryBlock(Block):
     embedding output again, x <- W [x ; embedding(token)] + step, ``step`` one row of a [passes, hidden] table.
 
     params: hidden, vocab, n_passes, index (which row of the table).  tensors: in_proj [hidden, 2 * hidden] (x first),
-    step [n_passes, hidden], embedding [vocab, hidden] (the model's token table).  No parts, no cache, no state."""
+    step [n_passes, hidden] (left out of the tensors: no such term), embedding [vocab, hidden] (the model's token table).
+    No parts, no cache, no state."""
     roles = {}
 
     def __init__(self, spec, runtime, parts):
@@ -119,14 +149,16 @@ class StreamReentryBlock(Block):
 
     def tensor_needs(self):
         t = self.spec.tensors
-        return {t["in_proj"]: TensorNeed((self.hidden, 2 * self.hidden)),
-                t["step"]: TensorNeed((self.n_passes, self.hidden)),
-                t["embedding"]: TensorNeed((self.vocab, self.hidden), "embedding")}
+        needs = {t["in_proj"]: TensorNeed((self.hidden, 2 * self.hidden)),
+                 t["embedding"]: TensorNeed((self.vocab, self.hidden), "embedding")}
+        if "step" in t:
+            needs[t["step"]] = TensorNeed((self.n_passes, self.hidden))
+        return needs
 
     def load(self, tensors):
         t = self.spec.tensors
         self.w_in = tensors[t["in_proj"]].contiguous()
-        self.step_row = tensors[t["step"]][self.index].contiguous()
+        self.step_row = tensors[t["step"]][self.index].contiguous() if "step" in t else None
         self.table = tensors[t["embedding"]]
 
     def flops_per_token(self) -> float:

@@ -32,14 +32,15 @@ class TokenEmbedding(Part):
 
 @register_part("head", "linear")
 class LinearHead(Part):
-    """params: vocab, width.  tensors: weight (names the token table when the head is tied, in
-    which case both parts hold the same device tensor)."""
+    """params: vocab, width, scale (default 1: the logits are multiplied by it, in float32).  tensors: weight (names
+    the token table when the head is tied, in which case both parts hold the same device tensor)."""
     chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def tensor_needs(self):
@@ -50,3 +51,5 @@ class LinearHead(Part):
 
     def forward(self, h, logits, n_rows, status=None):
         ops.linear(h, self.weight, logits, n_rows, status=status)
+        if self.scale != 1.0:
+            ops.scale_rows(logits, n_rows, self.scale)

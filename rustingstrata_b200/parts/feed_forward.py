@@ -64,3 +64,47 @@ class GatedMLP(FeedForward):
             ops.silu_mul(gate_up, act, T)
         ctx.owed = ops.linear(act, self.w_down, residual, T, accumulate=not ctx.store_output, status=ctx.status,
                               may_defer=ctx.may_owe and not ctx.store_output)
+
+
+@register_part("feed_forward", "activation_mlp")
+class ActivationMLP(FeedForward):
+    """down(act(up h)), no biases, with an activation that has learned numbers of its own.
+
+    params: hidden, intermediate, activation: "xielu" (two numbers p, q per layer: for z > 0, softplus(p) z^2 + z / 2;
+    for z <= 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2) or "gelu_tanh" (none).
+    tensors: up_proj, down_proj, and act [2] for xielu.  The activation's arithmetic is float32."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec.params["hidden"])
+        self.inter = int(spec.params["intermediate"])
+        self.activation = spec.params.get("activation", "xielu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation_mlp: activation '{self.activation}' has no kernel "
+                             f"(known: {', '.join(sorted(ops.ACTIVATIONS))})")
+        runtime.scratch("ff_act", runtime.max_batch_tokens, self.inter)
+        self.act_params = None
+
+    def tensor_needs(self):
+        t = self.spec.tensors
+        needs = {t["up_proj"]: TensorNeed((self.inter, self.hidden)), t["down_proj"]: TensorNeed((self.hidden, self.inter))}
+        if self.activation == "xielu":
+            needs[t["act"]] = TensorNeed((2,))
+        return needs
+
+    def load(self, tensors):
+        t = self.spec.tensors
+        self.w_up = tensors[t["up_proj"]].contiguous()
+        self.w_down = tensors[t["down_proj"]].contiguous()
+        if self.activation == "xielu":
+            self.act_params = tensors[t["act"]].to(torch.float32).contiguous()
+
+    def flops_per_token(self) -> float:
+        return 4.0 * self.hidden * self.inter
+
+    def forward(self, h, residual, ctx):
+        T = ctx.n_tokens
+        act = self.runtime.get_scratch("ff_act")[:, : self.inter]
+        ops.linear(h, self.w_up, act, T, status=ctx.status)
+        ops.activation(act, act, T, self.activation, self.act_params)
+        ops.linear(act, self.w_down, residual, T, accumulate=not ctx.store_output, status=ctx.status)

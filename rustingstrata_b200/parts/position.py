@@ -49,13 +49,29 @@ class NoPosition(PositionEncoding):
     cos_sin = None
 
 
+def scaled_frequencies(freq: np.ndarray, scaling) -> np.ndarray:
+    """Rotation frequencies rescaled by wavelength; ``scaling`` = (factor, low, high, original) or None."""
+    if scaling is None:
+        return freq
+    factor, low, high, original = scaling
+    wave = 2.0 * np.pi / freq
+    s = (original / wave - low) / (high - low)
+    blend = (1.0 - s) * freq / factor + s * freq
+    return np.where(wave < original / high, freq, np.where(wave > original / low, freq / factor, blend))
+
+
 @register_part("position", "rope_interleaved")
 class RotaryInterleaved(PositionEncoding):
     """Rotation of neighbouring pairs (2i, 2i + 1), i < n_rot / 2, by position * base^(-2i / n_rot).
 
-    params: n_rot, base.  The table has the layout of the NEOX kind ([position, cos(n_rot/2) | sin(n_rot/2)], float64
-    angles rounded to float32); what differs is which coordinates a kernel pairs, which ``pairing`` tells.  It holds
-    as many positions as a request can reach: the model's limit, or what the cache pool holds if that is less."""
+    params: n_rot, base, scaling (None, or {factor, low, high, original}: frequencies rescaled by wavelength).  The table
+    has the layout of the NEOX kind ([position, cos(n_rot/2) | sin(n_rot/2)], float64 angles rounded to float32); what
+    differs is which coordinates a kernel pairs, which ``pairing`` tells.  It holds as many positions as a request can
+    reach: the model's limit, or what the cache pool holds if that is less.
+
+    ``scaling`` stretches the slow rotations of a model trained on ``original`` positions: with wavelength
+    l = 2 pi / f, a frequency with l < original / high is kept, one with l > original / low becomes f / factor, and in
+    between, with s = (original / l - low) / (high - low), it becomes (1 - s) f / factor + s f."""
     chain_safe = True
     pairing = "interleaved"
 
@@ -65,8 +81,12 @@ class RotaryInterleaved(PositionEncoding):
         self.base = float(spec.params["base"])
         if self.n_rot % 2:
             raise ValueError(f"rope_interleaved: n_rot {self.n_rot} must be even")
+        sc = spec.params.get("scaling")
+        self.scaling = None if not sc else (float(sc["factor"]), float(sc["low"]), float(sc["high"]), float(sc["original"]))
+        if self.scaling is not None and (self.scaling[0] <= 0 or self.scaling[2] <= self.scaling[1] or self.scaling[3] <= 0):
+            raise ValueError(f"rope_interleaved: scaling needs factor > 0, high > low and original > 0, got {sc}")
         self.rows = max(1, min(runtime.max_positions, runtime.pool_tokens))
-        self._key = ("rope_interleaved", self.n_rot, self.base, self.rows)
+        self._key = ("rope_interleaved", self.n_rot, self.base, self.scaling, self.rows)
 
     @property
     def cos_sin(self) -> torch.Tensor:
@@ -74,7 +94,8 @@ class RotaryInterleaved(PositionEncoding):
 
     def _table(self) -> torch.Tensor:
         half = self.n_rot // 2
-        inv = np.power(np.float64(self.base), -2.0 * np.arange(half, dtype=np.float64) / self.n_rot)
+        inv = scaled_frequencies(np.power(np.float64(self.base), -2.0 * np.arange(half, dtype=np.float64) / self.n_rot),
+                                 self.scaling)
         theta = np.arange(self.rows, dtype=np.float64)[:, None] * inv[None, :]
         tab = np.concatenate([np.cos(theta), np.sin(theta)], axis=1).astype(np.float32)
         return torch.from_numpy(tab).to(self.runtime.device)

@@ -1,0 +1,158 @@
+"""Attention over a paged key/value cache whose scores are mixed across heads before the softmax, with a learned sink
+in every head's denominator and a sigmoid gate per head.
+
+Per token, from the mixer's input h:  q = W_q h + b_q (heads x dim), k = W_k h + b_k, v = W_v h + b_v (kv heads x dim /
+vdim; query head i reads kv head i // (heads / kv heads)).  Every q and k head is divided by its root mean square and
+multiplied by a weight of ``dim`` values shared by the heads; the position encoding then rotates the first ``n_rot``
+coordinates of each q and k head.  With raw[g, i, j] = (q_gi . k_gj) * scale the score of head h is
+
+    mixed[h, i, j] = sum_g talk[h, g] raw[g, i, j]                      (talk [heads, heads]; None: the raw score)
+
+and the weights of query i over the keys j <= i (within ``window`` if there is one) are
+
+    exp(mixed[h, i, j]) / (exp(sink[h]) + sum_j' exp(mixed[h, i, j']))  (sink [heads]; None: no such term).
+
+The sink has no key and no value, is neither scaled nor mixed, and counts once.  Head h's weighted sum of values is
+multiplied by sigmoid(w_g[h] . h), and W_o maps the joined heads back to the stream.  Norms, angles, scores, the mix,
+weights and gates are float32 in both engines; keys and values are cached in the engine's element type, in rows
+padded to a common size.  Each of bias, norm, talk, sink and gate is a parameter of the part and may be left out.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .base import CallInfo, HostBatch, Mixer, StepContext
+from .registry import register_part
+from .spec import CacheNeed, TensorNeed
+
+
+@register_part("mixer", "talking_attention")
+class TalkingAttention(Mixer):
+    """params: hidden, n_heads, n_kv_heads, dim, vdim, scale, eps, window (None: every key), bias, qk_norm, talk, sink,
+    gate (bools, default True).  tensors: q_proj, k_proj, v_proj, o_proj, and as the params ask q_bias, k_bias, v_bias,
+    q_norm, k_norm, talk [heads, heads], sink [heads], g_proj [heads, hidden]."""
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.n_heads, self.n_kv = int(p["n_heads"]), int(p["n_kv_heads"])
+        self.dk, self.dv = int(p["dim"]), int(p["vdim"])
+        self.scale = float(p["scale"])
+        self.eps = float(p.get("eps", 0.0))
+        self.window = int(p["window"]) if p.get("window") else 0
+        self.has_bias, self.qk_norm = bool(p.get("bias", True)), bool(p.get("qk_norm", True))
+        self.has_talk, self.has_sink, self.has_gate = bool(p.get("talk", True)), bool(p.get("sink", True)), bool(p.get("gate", True))
+        self.position = position
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"talking_attention: {self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
+        if max(self.dk, self.dv) > 256:
+            raise ValueError(f"talking_attention: head sizes {self.dk} / {self.dv} exceed the 256 the kernels take")
+        n_rot = int(getattr(position, "n_rot", 0) or 0)
+        if n_rot and getattr(position, "pairing", "") != "interleaved":
+            raise ValueError("talking_attention: its kernels rotate neighbouring pairs; the position encoding pairs otherwise")
+        if n_rot > self.dk:
+            raise ValueError(f"talking_attention: {n_rot} rotated coordinates in heads of {self.dk}")
+        self.head_pad = (max(self.dk, self.dv) + 7) // 8 * 8           # cache rows start on 16 bytes in both element types
+        self.q_cols, self.k_cols, self.v_cols = self.n_heads * self.dk, self.n_kv * self.dk, self.n_kv * self.dv
+        self.g_cols = self.n_heads if self.has_gate else 0
+        self.in_cols = self.q_cols + self.k_cols + self.v_cols + self.g_cols
+        self.o_in = self.n_heads * self.dv
+        self.q_per_cta = None
+        rt = runtime
+        rt.scratch("talk_proj", rt.max_batch_tokens, self.in_cols, torch.float32)
+        rt.scratch("talk_q", rt.max_batch_tokens, self.q_cols, torch.float32)
+        rt.scratch("talk_gate", 1, rt.max_batch_tokens * self.n_heads, torch.float32)      # flat: [T, heads] without a pitch
+        rt.scratch("talk_out", rt.max_batch_tokens, self.o_in)
+
+    # ---------------------------------------------------------------- weights
+    def tensor_needs(self):
+        t = self.spec.tensors
+        needs = {t["q_proj"]: TensorNeed((self.q_cols, self.hidden)), t["k_proj"]: TensorNeed((self.k_cols, self.hidden)),
+                 t["v_proj"]: TensorNeed((self.v_cols, self.hidden)), t["o_proj"]: TensorNeed((self.hidden, self.o_in))}
+        if self.has_bias:
+            needs.update({t["q_bias"]: TensorNeed((self.q_cols,)), t["k_bias"]: TensorNeed((self.k_cols,)),
+                          t["v_bias"]: TensorNeed((self.v_cols,))})
+        if self.qk_norm:
+            needs.update({t["q_norm"]: TensorNeed((self.dk,), "norm"), t["k_norm"]: TensorNeed((self.dk,), "norm")})
+        if self.has_talk:
+            needs[t["talk"]] = TensorNeed((self.n_heads, self.n_heads), "average")
+        if self.has_sink:
+            needs[t["sink"]] = TensorNeed((self.n_heads,))
+        if self.has_gate:
+            needs[t["g_proj"]] = TensorNeed((self.n_heads, self.hidden))
+        return needs
+
+    def load(self, tensors):
+        t = self.spec.tensors
+        mats = [tensors[t["q_proj"]], tensors[t["k_proj"]], tensors[t["v_proj"]]] + ([tensors[t["g_proj"]]] if self.has_gate else [])
+        if len({m.dtype for m in mats}) != 1:
+            raise ValueError("talking_attention: the input projections must share an element type")
+        self.w_in = torch.cat(mats, dim=0).contiguous()              # one [q | k | v | gate] matrix: h is read by one product
+        self.w_o = tensors[t["o_proj"]].contiguous()
+        f32 = lambda name: tensors[t[name]].to(torch.float32).contiguous()                        # noqa: E731
+        self.bias = torch.cat([f32("q_bias"), f32("k_bias"), f32("v_bias")]) if self.has_bias else None
+        self.q_norm_w = f32("q_norm") if self.qk_norm else None
+        self.k_norm_w = f32("k_norm") if self.qk_norm else None
+        self.talk = f32("talk") if self.has_talk else None
+        self.sink = f32("sink") if self.has_sink else None
+
+    # ---------------------------------------------------------------- what it keeps
+    def cache_need(self):
+        return CacheNeed(self.n_kv, self.head_pad, self.window or None)
+
+    def flops_per_token(self) -> float:
+        return 2.0 * self.hidden * (self.in_cols + self.o_in)
+
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        pairs = 0.0
+        for q, kv in zip(np.asarray(q_lens, dtype=np.int64), np.asarray(kv_lens, dtype=np.int64)):
+            pos = np.arange(kv - q, kv, dtype=np.float64)
+            pairs += float((pos + 1 if not self.window else np.minimum(pos + 1, self.window)).sum())
+        mix = 2.0 * self.n_heads * self.n_heads if self.has_talk else 0.0
+        return (2.0 * self.n_heads * (self.dk + self.dv) + mix) * pairs
+
+    # ---------------------------------------------------------------- planning
+    def plan_key(self):
+        if self.q_per_cta is None:
+            self.q_per_cta = ops.talking_attention_q_per_cta(self.n_heads, self.dk, self.dv)
+        return ("talking_attention", self.q_per_cta)
+
+    def build_plan(self, batch: HostBatch):
+        """Tiles of up to q_per_cta neighbouring queries of one sequence, the ones with the most keys to walk first."""
+        qt = self.q_per_cta
+        tiles = []
+        for s in range(batch.n_seqs):
+            offs = np.arange(0, batch.q_lens[s], qt, dtype=np.int32)
+            tiles.append(np.stack([np.full_like(offs, s), offs], axis=1))
+        work = np.concatenate(tiles, axis=0).astype(np.int32)
+        if len(work) > 1 and not batch.bucketed:
+            last = batch.kv_lens[work[:, 0]] - batch.q_lens[work[:, 0]] + work[:, 1]
+            work = work[np.argsort(-last, kind="stable")]
+        return {"work": work.reshape(-1), "n_work": int(work.shape[0])}
+
+    # ---------------------------------------------------------------- the step
+    def forward(self, h, residual, ctx: StepContext, call: CallInfo):
+        rt, T = self.runtime, ctx.n_tokens
+        if not call.writes_cache:
+            raise RuntimeError("talking_attention: every call owns its cache")
+        proj = rt.get_scratch("talk_proj", torch.float32)[:, : self.in_cols]
+        q = rt.get_scratch("talk_q", torch.float32)[:, : self.q_cols]
+        gate = rt.get_scratch("talk_gate", torch.float32)[0, : rt.max_batch_tokens * self.n_heads] \
+            .view(rt.max_batch_tokens, self.n_heads) if self.has_gate else None
+        out = rt.get_scratch("talk_out")[:, : self.o_in]
+        ops.linear(h, self.w_in, proj, T, status=ctx.status)
+        table = ctx.block_tables[call.cache_group]
+        pos = self.position
+        rot = getattr(pos, "cos_sin", None) if pos is not None else None
+        ops.talking_attention_prep(proj, self.bias, self.q_norm_w, self.k_norm_w, self.eps, rot,
+                                   int(pos.n_rot) if rot is not None else 0, q, gate, call.cache, table, rt.page_size,
+                                   ctx.positions, ctx.seq_of_token, self.n_heads, self.n_kv, self.dk, self.dv, T, True, ctx.status)
+        plan = ctx.plans[self.plan_key()]
+        ops.talking_attention(q, gate, call.cache, table, rt.page_size, ctx.q_start, ctx.kv_len, plan["work"], plan["n_work"],
+                              self.talk, self.sink, out, self.n_heads, self.n_kv, self.dk, self.dv, self.window,
+                              # a step of single tokens: a CTA's shared memory is sized for its one query
+                              1 if int(ctx.host.q_lens.max()) == 1 else self.q_per_cta, self.scale, ctx.status)
+        ops.linear(out, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)
