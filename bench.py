@@ -95,8 +95,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run this many of the configuration's layers (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
-    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex", "tabedra"])
-    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex or tabedra: widths to run")
+    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex", "tabedra", "kupelix"])
+    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex, tabedra or kupelix: widths to run")
     ap.add_argument("--marginal", action="store_true", help="marginal cost of each kernel family inside the decode step")
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="with --marginal: tokens each request holds")
     ap.add_argument("--marginal-prefill", action="store_true",
@@ -121,8 +121,8 @@ def main() -> int:
         return long_context_workload(args)
     if args.workload == "lokinex":
         return lokinex_workload(args)
-    if args.workload == "tabedra":
-        return lokinex_workload(args, design="tabedra")
+    if args.workload in ("tabedra", "kupelix"):
+        return lokinex_workload(args, design=args.workload)
 
     import numpy as np
     import torch
@@ -401,6 +401,23 @@ def tabedra_config(width: int) -> dict:
             "layers": layers}
 
 
+def kupelix_config(width: int) -> dict:
+    """A Kupelix model whose layers resemble real ones at this width: heads of 128 query/key and 128 value coordinates
+    in all three mixers; attention with one key/value head per four query heads and half of each head rotated; the delta
+    rule with one query/key head per two state heads, 4 taps and low-rank maps of 64; a dense feed-forward of 4 x width
+    in every layer; four layers (attention, delta rule, HGRN2, attention) run twice by the loop."""
+    heads = width // 128
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                          "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 64}}}
+    delta = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128,
+                                                "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    hgrn = {"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Kupelix", "vocab": 32768, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "layers": [dict(att, mlp=dense), dict(delta, mlp=dense), dict(hgrn, mlp=dense), dict(att, mlp=dense)],
+            "loop": {"start": 0, "stop": 4, "times": 2}}
+
+
 def qwen3_windowed(width: int) -> dict:
     """The closest existing model for the Tabedra design: the Qwen3 decoder of :func:`qwen3_like` with the same sliding
     window on every layer and as many key/value heads."""
@@ -424,7 +441,8 @@ class OpTimer:
              "gated_linear_recurrence_gates", "latent_kv_write", "relu_squared", "moe_route", "grouped_linear", "moe_combine",
              "grouped_gemm_mma", "attention_latent", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
              "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand", "embed_sum", "stream_layernorm",
-             "stream_update", "router_topk", "conv_norm_kv_write", "sigmoid_gate")
+             "stream_update", "router_topk", "conv_norm_kv_write", "sigmoid_gate", "talking_attention_prep", "talking_attention",
+             "state_recurrence", "hgrn2_prep", "delta_prep", "head_norm_gate", "activation", "scale_rows")
 
     def __init__(self):
         self.events, self.real = [], {}
@@ -477,7 +495,8 @@ def lokinex_workload(args, design: str = "lokinex") -> int:
     pk = roofline.peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
     clocks = ClockSampler()
     clocks.start()
-    pair = {"lokinex": (lokinex_config, qwen3_like), "tabedra": (tabedra_config, qwen3_windowed)}[design]
+    pair = {"lokinex": (lokinex_config, qwen3_like), "tabedra": (tabedra_config, qwen3_windowed),
+            "kupelix": (kupelix_config, qwen3_like)}[design]
     out = {"workload": design, "prompt_len": PROMPT, "batch": args.batch, "steps": args.steps, "dtype": "bf16",
            "data": "synthetic", "weights": "random N(0,0.02) bf16", "peaks": pk["source"], "sizes": {}}
     for width in [int(x) for x in args.sizes.split(",")]:
