@@ -37,7 +37,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "stream": {"sources": ["stream_parts.cu", "conv_attention_parts.cu"], "link": []},
     # mixers that keep a state matrix per head (gated write, delta rule), attention with scores mixed across heads,
     # a sink and head gates, and the activations that go with them (both engines)
-    "mixers": {"sources": ["state_mixers.cu", "talking_attention.cu"], "link": []},
+    "mixers": {"sources": ["state_mixers.cu", "talking_attention.cu", "talking_attention_mma.cu"], "link": []},
     # tensor-core paths of the bfloat16 engine; the 32-bit engine never loads this library
     # not loaded by the engine: one kernel whose wait is never satisfied, built with a 2 ms limit, so that a test can
     # see the bounded-wait path end in a status bit and leave the context usable

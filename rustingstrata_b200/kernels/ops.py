@@ -1554,6 +1554,11 @@ def mixerslib():
         lib.rs_talking_attention.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_long, c_int,
                                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+        lib.rs_talking_attention_mma_q_per_cta.argtypes = [c_int, c_int, c_int, c_int]
+        lib.rs_talking_attention_mma.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int,
+                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                 c_void_p, c_void_p]
         _mixerslib = lib
     return _mixerslib
 
@@ -1746,3 +1751,45 @@ def talking_attention(q: torch.Tensor, gate: Optional[torch.Tensor], cache: torc
         cache.shape[-1], _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, _ptr(talk),
         _ptr(sink), _ptr(out), dtype_code(out), out.stride(0), n_heads, n_kv, dk, dv, window, q_per_cta, float(scale),
         _ptr(status), _stream()), "talking_attention")
+
+
+def talking_attention_mma_q_per_cta(n_heads: int, n_kv: int, dk: int, dv: int) -> int:
+    """Queries a CTA of the tensor-core form takes for these sizes; 0 when the shape is not one of its shapes (head sizes
+    that are no multiple of 16, more than 32 heads, values wider than 128 or than 64 with more than 16 heads)."""
+    return int(mixerslib().rs_talking_attention_mma_q_per_cta(n_heads, n_kv, dk, dv))
+
+
+TALKING_WORK_COLS = 5          # sequence, first query, part, parts, first row of the tile's partial sums
+
+
+def talking_attention_mma(q: torch.Tensor, gate: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
+                          page_size: int, q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int,
+                          any_parts: bool, talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], out: torch.Tensor,
+                          partial: Optional[torch.Tensor], n_heads: int, n_kv: int, dk: int, dv: int, window: int, q_per_cta: int,
+                          scale: float, status: torch.Tensor) -> None:
+    """``talking_attention`` for a bfloat16 cache on the tensor cores (csrc/talking_attention_mma.cu).  ``work`` rows are
+    (sequence, first query, part, parts, first partial row): a tile's key tiles are dealt out over ``parts`` CTAs, whose
+    sums meet in ``partial`` float32 [rows, >= heads * (dv + 2)] (part p of a tile of n queries uses rows first + p * n ..)."""
+    _cuda(q, gate, cache, block_table, q_start, kv_len, work, talk, sink, out, partial, status)
+    _f32_rows("talking_attention_mma", q=q, gate=gate, partial=partial)
+    _rows_contiguous(out, "talking_attention_mma out")
+    _i32("talking_attention_mma", block_table, q_start, kv_len, work)
+    if cache.dtype != torch.bfloat16:
+        raise KernelError("talking_attention_mma: the cache must be bfloat16")
+    for name, t, n in (("talk", talk, n_heads * n_heads), ("sink", sink, n_heads)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError(f"talking_attention_mma: {name} must be contiguous float32 with {n} values")
+    if q.shape[1] < n_heads * dk or out.shape[1] < n_heads * dv or work.numel() < TALKING_WORK_COLS * n_work \
+            or not cache.is_contiguous() or (gate is not None and (gate.shape[1] != n_heads or not gate.is_contiguous())) \
+            or out.stride(0) % 2 or out.data_ptr() % 8:
+        raise KernelError("talking_attention_mma: shapes do not fit the head counts and sizes")
+    rows = 0
+    if partial is not None:
+        if not partial.is_contiguous() or partial.shape[1] < n_heads * (dv + 2):
+            raise KernelError("talking_attention_mma: the partial sums need contiguous rows of heads * (dv + 2) values")
+        rows = partial.numel() // (n_heads * (dv + 2))
+    _check(mixerslib().rs_talking_attention_mma(
+        _ptr(q), q.stride(0), _ptr(gate), _ptr(cache), cache.stride(0), cache.shape[0], page_size, cache.shape[-1],
+        _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, 1 if any_parts else 0,
+        _ptr(talk), _ptr(sink), _ptr(out), dtype_code(out), out.stride(0), _ptr(partial), rows, n_heads, n_kv, dk, dv, window,
+        q_per_cta, float(scale), _ptr(status), _stream()), "talking_attention_mma")

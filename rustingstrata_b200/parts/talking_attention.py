@@ -28,6 +28,14 @@ from .registry import register_part
 from .spec import CacheNeed, TensorNeed
 
 
+KEY_TILE = 32              # keys per tile of the tensor-core form
+MMA_SINGLE_Q = 4           # its query tile in a step of single tokens (the smallest it has: more CTAs fit a multiprocessor)
+FILL_CTAS = 296            # two per multiprocessor: a step with fewer tiles than half of this shares out its keys
+MAX_PARTS = 32
+MIN_PART_TILES = 4         # a part walks at least this many key tiles
+PARTIAL_ROWS = 4096        # (query, part) rows of partial sums the workspace holds
+
+
 @register_part("mixer", "talking_attention")
 class TalkingAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, dim, vdim, scale, eps, window (None: every key), bias, qk_norm, talk, sink,
@@ -61,7 +69,10 @@ class TalkingAttention(Mixer):
         self.in_cols = self.q_cols + self.k_cols + self.v_cols + self.g_cols
         self.o_in = self.n_heads * self.dv
         self.q_per_cta = None
+        self.mma_q = 0
         rt = runtime
+        if not rt.precise:
+            rt.scratch("talk_partial", PARTIAL_ROWS, self.n_heads * (self.dv + 2), torch.float32)
         rt.scratch("talk_proj", rt.max_batch_tokens, self.in_cols, torch.float32)
         rt.scratch("talk_q", rt.max_batch_tokens, self.q_cols, torch.float32)
         rt.scratch("talk_gate", 1, rt.max_batch_tokens * self.n_heads, torch.float32)      # flat: [T, heads] without a pitch
@@ -115,23 +126,52 @@ class TalkingAttention(Mixer):
         return (2.0 * self.n_heads * (self.dk + self.dv) + mix) * pairs
 
     # ---------------------------------------------------------------- planning
-    def plan_key(self):
+    def _setup(self):
         if self.q_per_cta is None:
             self.q_per_cta = ops.talking_attention_q_per_cta(self.n_heads, self.dk, self.dv)
-        return ("talking_attention", self.q_per_cta)
+            # the tensor-core form reads a bfloat16 cache; the 32-bit engine and shapes it does not take use the other
+            self.mma_q = 0 if self.runtime.precise else ops.talking_attention_mma_q_per_cta(self.n_heads, self.n_kv, self.dk, self.dv)
+
+    def plan_key(self):
+        self._setup()
+        return ("talking_attention", self.q_per_cta, self.mma_q, self.window)
 
     def build_plan(self, batch: HostBatch):
-        """Tiles of up to q_per_cta neighbouring queries of one sequence, the ones with the most keys to walk first."""
-        qt = self.q_per_cta
+        """Tiles of neighbouring queries of one sequence, the ones with the most keys to walk first.  For the tensor-core
+        form a tile's key tiles are dealt out over several CTAs when the step has too few tiles to fill the device."""
+        self._setup()
+        single = int(batch.q_lens.max()) == 1
+        qt = (MMA_SINGLE_Q if single else self.mma_q) if self.mma_q else (1 if single else self.q_per_cta)
         tiles = []
         for s in range(batch.n_seqs):
             offs = np.arange(0, batch.q_lens[s], qt, dtype=np.int32)
             tiles.append(np.stack([np.full_like(offs, s), offs], axis=1))
         work = np.concatenate(tiles, axis=0).astype(np.int32)
+        first = batch.kv_lens[work[:, 0]] - batch.q_lens[work[:, 0]] + work[:, 1]        # position of the tile's first query
         if len(work) > 1 and not batch.bucketed:
-            last = batch.kv_lens[work[:, 0]] - batch.q_lens[work[:, 0]] + work[:, 1]
-            work = work[np.argsort(-last, kind="stable")]
-        return {"work": work.reshape(-1), "n_work": int(work.shape[0])}
+            order = np.argsort(-first, kind="stable")
+            work, first = work[order], first[order]
+        if not self.mma_q:
+            return {"work": work.reshape(-1), "n_work": int(work.shape[0]), "any_parts": 0, "qt": qt}
+        n = work.shape[0]
+        nq = np.minimum(qt, batch.q_lens[work[:, 0]] - work[:, 1])
+        parts = np.ones(n, dtype=np.int64)
+        if n < FILL_CTAS // 2:
+            share = min(MAX_PARTS, FILL_CTAS // n)
+            if batch.bucketed:
+                parts[:] = share              # a captured step: the launch shape must not follow the lengths
+            else:
+                begin = np.maximum(0, first - self.window + 1) if self.window else np.zeros(n, dtype=np.int64)
+                key_tiles = -(-(first + nq) // KEY_TILE) - begin // KEY_TILE
+                parts = np.clip(key_tiles // MIN_PART_TILES, 1, share)
+            while int((parts * nq)[parts > 1].sum()) > PARTIAL_ROWS:
+                parts = np.maximum(1, parts // 2)
+        rows = np.where(parts > 1, parts * nq, 0)
+        base = np.concatenate([[0], np.cumsum(rows)[:-1]])
+        rep = np.repeat(np.arange(n), parts)
+        part = np.arange(len(rep)) - np.repeat(np.cumsum(parts) - parts, parts)
+        full = np.stack([work[rep, 0], work[rep, 1], part, parts[rep], base[rep]], axis=1).astype(np.int32)
+        return {"work": full.reshape(-1), "n_work": int(full.shape[0]), "any_parts": int(bool((parts > 1).any())), "qt": qt}
 
     # ---------------------------------------------------------------- the step
     def forward(self, h, residual, ctx: StepContext, call: CallInfo):
@@ -151,8 +191,14 @@ class TalkingAttention(Mixer):
                                    int(pos.n_rot) if rot is not None else 0, q, gate, call.cache, table, rt.page_size,
                                    ctx.positions, ctx.seq_of_token, self.n_heads, self.n_kv, self.dk, self.dv, T, True, ctx.status)
         plan = ctx.plans[self.plan_key()]
-        ops.talking_attention(q, gate, call.cache, table, rt.page_size, ctx.q_start, ctx.kv_len, plan["work"], plan["n_work"],
-                              self.talk, self.sink, out, self.n_heads, self.n_kv, self.dk, self.dv, self.window,
-                              # a step of single tokens: a CTA's shared memory is sized for its one query
-                              1 if int(ctx.host.q_lens.max()) == 1 else self.q_per_cta, self.scale, ctx.status)
+        if self.mma_q:
+            partial = rt.get_scratch("talk_partial", torch.float32) if plan["any_parts"] else None
+            ops.talking_attention_mma(q, gate, call.cache, table, rt.page_size, ctx.q_start, ctx.kv_len, plan["work"],
+                                      plan["n_work"], bool(plan["any_parts"]), self.talk, self.sink, out, partial, self.n_heads,
+                                      self.n_kv, self.dk, self.dv, self.window, plan["qt"], self.scale, ctx.status)
+        else:
+            # a step of single tokens: a CTA's shared memory is sized for its one query
+            ops.talking_attention(q, gate, call.cache, table, rt.page_size, ctx.q_start, ctx.kv_len, plan["work"],
+                                  plan["n_work"], self.talk, self.sink, out, self.n_heads, self.n_kv, self.dk, self.dv,
+                                  self.window, plan["qt"], self.scale, ctx.status)
         ops.linear(out, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)
