@@ -441,7 +441,7 @@ class OpTimer:
              "gated_linear_recurrence_gates", "latent_kv_write", "relu_squared", "moe_route", "grouped_linear", "moe_combine",
              "grouped_gemm_mma", "attention_latent", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
              "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand", "embed_sum", "stream_layernorm",
-             "stream_update", "router_topk", "conv_norm_kv_write", "sigmoid_gate", "talking_attention_prep", "talking_attention",
+             "stream_update", "router_topk", "conv_norm_kv_write", "sigmoid_gate", "talking_attention_prep", "talking_attention", "talking_attention_mma",
              "state_recurrence", "hgrn2_prep", "delta_prep", "head_norm_gate", "activation", "scale_rows")
 
     def __init__(self):

@@ -49,71 +49,144 @@ __device__ __forceinline__ float sum_row_lanes(float v) {
     return v;
 }
 
+// Lane rl of a column keeps rows 32 i + 4 rl .. + 3 for i < RPT / 4: the eight lanes of a column read 128 neighbouring
+// bytes at a time, from shared memory without bank conflicts and from the state in whole lines.
 template <int RPT>
 __device__ __forceinline__ void load_rows(const float* p, float* r) {
 #pragma unroll
     for (int m = 0; m < RPT; m += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(p + m);
+        const float4 a = *reinterpret_cast<const float4*>(p + m * ROW_LANES);
         r[m] = a.x; r[m + 1] = a.y; r[m + 2] = a.z; r[m + 3] = a.w;
     }
 }
 
+// The step's per-token inputs (q, k, g rows of the head, the CTA's 32 values, the write strength) reach the token loop
+// through shared memory, a chunk of tokens at a time with cp.async, one chunk ahead of the one being walked: the loop
+// itself waits for nothing but its own arithmetic.  For the delta rule both sums over rows of a token are taken from
+// the decayed state S' = diag(g) S in one round of shuffles: with r = S'^T k and a = S'^T q, u = beta (v - r) and the
+// read-out of S' + k u^T is a + u (k . q).
+template <int RPT> struct RecurrenceStage {
+    static constexpr int RP = RPT * ROW_LANES;
+    static constexpr int CHUNK = RPT <= 16 ? 16 : 8;                  // tokens per buffer
+    static constexpr int ROW = 3 * RP + COLS_PER_CTA + 4;              // q | k | g | v of the CTA's columns | beta, pad
+    static constexpr size_t BYTES = 2ull * CHUNK * ROW * sizeof(float);
+};
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
 template <int RPT, bool DELTA>
 __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams p) {
-    constexpr int RP = RPT * ROW_LANES;                  // padded rows of a head
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    using St = RecurrenceStage<RPT>;
+    constexpr int RP = St::RP, CHUNK = St::CHUNK, ROW = St::ROW;
+    extern __shared__ __align__(16) float stage[];         // [2][CHUNK][ROW]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rl = lane & 7, cl = lane >> 3;
     const int s = blockIdx.x / p.heads, h = blockIdx.x % p.heads;
-    const int j = blockIdx.y * COLS_PER_CTA + warp * 4 + cl;
+    const int nthreads = blockDim.x, cols_cta = blockDim.x / ROW_LANES;      // a CTA walks 8, 16 or 32 columns
+    const int jl = warp * 4 + cl;                           // column within the CTA
+    const int j = blockIdx.y * cols_cta + jl;
     const bool live = j < p.columns;
     const int jc = live ? j : p.columns - 1;              // lanes beyond the last column walk it too and store nothing
     const int t0 = p.q_start[s], t1 = p.q_start[s + 1];
-    float* sp = p.state + (size_t)p.slots[s] * p.state_stride + ((size_t)h * p.columns + jc) * RP + rl * RPT;
+    const int n = t1 - t0;
+    float* sp = p.state + (size_t)p.slots[s] * p.state_stride + ((size_t)h * p.columns + jc) * RP + rl * 4;
     float S[RPT];
     load_rows<RPT>(sp, S);
-    const size_t qk_off = (size_t)(DELTA ? h / p.group : h) * RP + rl * RPT;
-    const size_t k_off = DELTA ? qk_off : (size_t)h * RP + rl * RPT;
-    const size_t g_off = (size_t)h * RP + rl * RPT;
-    float qn[RPT], kn[RPT], gn[RPT];
-    float vn = 0.f, bn = 0.f;
-    if (t0 < t1) {
-        load_rows<RPT>(p.q + (size_t)t0 * p.q_stride + qk_off, qn);
-        load_rows<RPT>(p.k + (size_t)t0 * p.k_stride + k_off, kn);
-        load_rows<RPT>(p.g + (size_t)t0 * p.g_stride + g_off, gn);
-        vn = p.v[(size_t)t0 * p.v_stride + (size_t)h * p.columns + jc];
-        if (DELTA) bn = p.beta[(size_t)t0 * p.beta_stride + h];
-    }
-    for (int t = t0; t < t1; ++t) {
-        float qc[RPT], kc[RPT], gc[RPT];
-#pragma unroll
-        for (int m = 0; m < RPT; ++m) { qc[m] = qn[m]; kc[m] = kn[m]; gc[m] = gn[m]; }
-        const float vc = vn, bc = bn;
-        if (t + 1 < t1) {                                  // the next token's rows are on their way while this one is worked
-            load_rows<RPT>(p.q + (size_t)(t + 1) * p.q_stride + qk_off, qn);
-            load_rows<RPT>(p.k + (size_t)(t + 1) * p.k_stride + k_off, kn);
-            load_rows<RPT>(p.g + (size_t)(t + 1) * p.g_stride + g_off, gn);
-            vn = p.v[(size_t)(t + 1) * p.v_stride + (size_t)h * p.columns + jc];
-            if (DELTA) bn = p.beta[(size_t)(t + 1) * p.beta_stride + h];
+    const size_t q_off = (size_t)(DELTA ? h / p.group : h) * RP;
+    const size_t k_off = DELTA ? q_off : (size_t)h * RP;
+    const size_t g_off = (size_t)h * RP;
+
+    auto fetch = [&](int c) {                               // chunk c of the step's tokens into buffer c & 1
+        float* dst = stage + (size_t)(c & 1) * CHUNK * ROW;
+        const int first = t0 + c * CHUNK, count = min(CHUNK, n - c * CHUNK);
+        constexpr int PER = RP / 4;                         // 16-byte pieces of a row of q, k or g
+        for (int i = tid; i < count * 3 * PER; i += nthreads) {
+            const int tt = i / (3 * PER), rest = i % (3 * PER), which = rest / PER, piece = rest % PER;
+            const size_t t = first + tt;
+            const float* src = which == 0 ? p.q + t * p.q_stride + q_off
+                             : which == 1 ? p.k + t * p.k_stride + k_off : p.g + t * p.g_stride + g_off;
+            cp_async_16(dst + tt * ROW + which * RP + piece * 4, src + piece * 4);
         }
-        float acc = 0.f;
-        if (DELTA) {
-            float r = 0.f;
-#pragma unroll
-            for (int m = 0; m < RPT; ++m) { S[m] *= gc[m]; r = fmaf(S[m], kc[m], r); }
-            r = sum_row_lanes(r);
-            const float u = bc * (vc - r);
-#pragma unroll
-            for (int m = 0; m < RPT; ++m) { S[m] = fmaf(kc[m], u, S[m]); acc = fmaf(S[m], qc[m], acc); }
+        for (int i = tid; i < count * (cols_cta + 1); i += nthreads) {
+            const int tt = i / (cols_cta + 1), c2 = i % (cols_cta + 1);
+            const size_t t = first + tt;
+            if (c2 < cols_cta) {
+                const int col = min((int)blockIdx.y * cols_cta + c2, p.columns - 1);
+                cp_async_4(dst + tt * ROW + 3 * RP + c2, p.v + t * p.v_stride + (size_t)h * p.columns + col);
+            } else if (DELTA) {
+                cp_async_4(dst + tt * ROW + 3 * RP + COLS_PER_CTA, p.beta + t * p.beta_stride + h);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const int chunks = (n + CHUNK - 1) / CHUNK;
+    if (chunks > 0) fetch(0);
+    for (int c = 0; c < chunks; ++c) {
+        if (c + 1 < chunks) {
+            fetch(c + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
-#pragma unroll
-            for (int m = 0; m < RPT; ++m) { S[m] = fmaf(gc[m], S[m], kc[m] * vc); acc = fmaf(S[m], qc[m], acc); }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        acc = sum_row_lanes(acc);
-        if (rl == 0 && live) p.out[(size_t)t * p.out_stride + (size_t)h * p.columns + j] = acc;
+        __syncthreads();
+        float* buf = stage + (size_t)(c & 1) * CHUNK * ROW;
+        const int count = min(CHUNK, n - c * CHUNK);
+        if (DELTA) {                                        // k . q of every token of the chunk, once for all columns
+            constexpr int TEAM = 4;                         // lanes per token, whatever the CTA's width: one order of additions
+            const int tt = tid / TEAM, part = tid % TEAM;
+            float d = 0.f;
+            if (tt < count)
+                for (int i = part; i < RP; i += TEAM) d = fmaf(buf[tt * ROW + i], buf[tt * ROW + RP + i], d);
+#pragma unroll
+            for (int o = TEAM / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            if (part == 0 && tt < count) buf[tt * ROW + 3 * RP + COLS_PER_CTA + 1] = d;
+            __syncthreads();
+        }
+        for (int tt = 0; tt < count; ++tt) {
+            const float* row = buf + tt * ROW;
+            float qc[RPT], kc[RPT], gc[RPT];
+            load_rows<RPT>(row + rl * 4, qc);
+            load_rows<RPT>(row + RP + rl * 4, kc);
+            load_rows<RPT>(row + 2 * RP + rl * 4, gc);
+            const float vc = row[3 * RP + jl];
+            float acc;
+            if (DELTA) {
+                const float bc = row[3 * RP + COLS_PER_CTA], d = row[3 * RP + COLS_PER_CTA + 1];
+                float r4[4] = {0.f, 0.f, 0.f, 0.f}, a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int m = 0; m < RPT; ++m) {
+                    S[m] *= gc[m];
+                    r4[m & 3] = fmaf(S[m], kc[m], r4[m & 3]);
+                    a4[m & 3] = fmaf(S[m], qc[m], a4[m & 3]);
+                }
+                float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+                float a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+                r = sum_row_lanes(r);
+                a = sum_row_lanes(a);
+                const float u = bc * (vc - r);
+#pragma unroll
+                for (int m = 0; m < RPT; ++m) S[m] = fmaf(kc[m], u, S[m]);
+                acc = fmaf(u, d, a);
+            } else {
+                float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int m = 0; m < RPT; ++m) { S[m] = fmaf(gc[m], S[m], kc[m] * vc); a4[m & 3] = fmaf(S[m], qc[m], a4[m & 3]); }
+                acc = sum_row_lanes((a4[0] + a4[1]) + (a4[2] + a4[3]));
+            }
+            if (rl == 0 && live) p.out[(size_t)(t0 + c * CHUNK + tt) * p.out_stride + (size_t)h * p.columns + j] = acc;
+        }
+        __syncthreads();                                    // the buffer is refilled two chunks on
     }
     if (live) {
 #pragma unroll
-        for (int m = 0; m < RPT; m += 4) *reinterpret_cast<float4*>(sp + m) = make_float4(S[m], S[m + 1], S[m + 2], S[m + 3]);
+        for (int m = 0; m < RPT; m += 4)
+            *reinterpret_cast<float4*>(sp + m * ROW_LANES) = make_float4(S[m], S[m + 1], S[m + 2], S[m + 3]);
     }
 }
 
@@ -270,20 +343,38 @@ __global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* o, lon
 enum Activation : int { ACT_XIELU = 0, ACT_GELU_TANH = 1 };
 
 // xIELU with two learned numbers (p, q): z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+__device__ __forceinline__ float activate(float z, int kind, float ap, float an) {
+    if (kind == ACT_XIELU) return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
 template <typename T>
 __global__ void activation_kernel(const T* x, long x_stride, T* out, long out_stride, int width, long n, int kind, const void* pq, int pq_dt) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     const long t = idx / width; const int c = (int)(idx % width);
-    const float z = to_f32<T>(x[t * x_stride + c]);
-    float y;
-    if (kind == ACT_XIELU) {
-        const float ap = softplus_f(load_any(pq, pq_dt, 0)), an = 0.5f + softplus_f(load_any(pq, pq_dt, 1));
-        y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
-    } else {
-        y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    float ap = 0.f, an = 0.f;
+    if (kind == ACT_XIELU) { ap = softplus_f(load_any(pq, pq_dt, 0)); an = 0.5f + softplus_f(load_any(pq, pq_dt, 1)); }
+    out[t * out_stride + c] = from_f32<T>(activate(to_f32<T>(x[t * x_stride + c]), kind, ap, an));
+}
+
+// 16 bytes per thread and step (rows that start on 16 bytes, a width that is a multiple of the 16 bytes' elements)
+template <typename T>
+__global__ void __launch_bounds__(256) activation_vec_kernel(const T* x, long x_stride, T* out, long out_stride, int width, int n_rows,
+                                                             int kind, const void* pq, int pq_dt) {
+    constexpr int V = 16 / sizeof(T);
+    float ap = 0.f, an = 0.f;
+    if (kind == ACT_XIELU) { ap = softplus_f(load_any(pq, pq_dt, 0)); an = 0.5f + softplus_f(load_any(pq, pq_dt, 1)); }
+    const int per_row = width / V;
+    const long total = (long)n_rows * per_row;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long t = i / per_row; const int c = (int)(i % per_row) * V;
+        uint4 raw = *reinterpret_cast<const uint4*>(x + t * x_stride + c);
+        T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < V; ++j) e[j] = from_f32<T>(activate(to_f32<T>(e[j]), kind, ap, an));
+        *reinterpret_cast<uint4*>(out + t * out_stride + c) = raw;
     }
-    out[t * out_stride + c] = from_f32<T>(y);
 }
 
 __global__ void scale_rows_kernel(float* x, long stride, int width, long n, float scale) {
@@ -307,11 +398,27 @@ RS_EXPORT int rs_state_recurrence(const float* q, long q_stride, const float* k,
     if (n_seqs <= 0) return 0;
     RecurrenceParams p{q, q_stride, k, k_stride, g, g_stride, beta, beta_stride, v, v_stride, out, out_stride, state, state_stride,
                        q_start, slots, heads, group < 1 ? 1 : group, columns};
-    const dim3 grid(n_seqs * heads, (columns + COLS_PER_CTA - 1) / COLS_PER_CTA);
-#define RS_REC(RPT)                                                                                   \
-    case RPT * ROW_LANES:                                                                             \
-        if (delta) state_recurrence_kernel<RPT, true><<<grid, 256, 0, stream>>>(p);                   \
-        else state_recurrence_kernel<RPT, false><<<grid, 256, 0, stream>>>(p);                        \
+    // narrower CTAs when the step has few (sequence, head) pairs: the walk is a chain of dependent steps, so its time is
+    // that of one CTA, and more of them only cost reads of q, k and g that the second-level cache serves
+    int cols_cta = COLS_PER_CTA;
+    while (cols_cta > 8 && (long)n_seqs * heads * ((columns + cols_cta - 1) / cols_cta) < 2 * 148) cols_cta >>= 1;
+    const dim3 grid(n_seqs * heads, (columns + cols_cta - 1) / cols_cta);
+    const int threads = cols_cta * ROW_LANES;
+    static bool sized = false;          // once: the attribute is a property of the function, not of a launch
+#define RS_REC_SIZE(RPT)                                                                                                        \
+    cudaFuncSetAttribute(state_recurrence_kernel<RPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
+                         (int)RecurrenceStage<RPT>::BYTES);                                                                     \
+    cudaFuncSetAttribute(state_recurrence_kernel<RPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,                     \
+                         (int)RecurrenceStage<RPT>::BYTES);
+    if (!sized) {
+        RS_REC_SIZE(4) RS_REC_SIZE(8) RS_REC_SIZE(16) RS_REC_SIZE(32)
+        sized = true;
+    }
+#undef RS_REC_SIZE
+#define RS_REC(RPT)                                                                                                    \
+    case RPT * ROW_LANES:                                                                                              \
+        if (delta) state_recurrence_kernel<RPT, true><<<grid, threads, RecurrenceStage<RPT>::BYTES, stream>>>(p);      \
+        else state_recurrence_kernel<RPT, false><<<grid, threads, RecurrenceStage<RPT>::BYTES, stream>>>(p);           \
         break;
     switch (rows_pad) {
         RS_REC(4) RS_REC(8) RS_REC(16) RS_REC(32)
@@ -365,6 +472,14 @@ RS_EXPORT int rs_activation(const void* x, long x_stride, void* out, long out_st
     const long n = (long)n_rows * width;
     if (n <= 0) return 0;
     if (kind == ACT_XIELU && !pq) return (int)cudaErrorInvalidValue;
+    const int esz = dt == RS_F32 ? 4 : 2, v = 16 / esz;
+    if (width % v == 0 && x_stride % v == 0 && out_stride % v == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const long pieces = n / v;
+        const unsigned blocks = (unsigned)((pieces + 255) / 256 < 148 * 16 ? (pieces + 255) / 256 : 148 * 16);
+        RS_DISPATCH_DTYPE(dt, T, (activation_vec_kernel<T><<<blocks, 256, 0, stream>>>(
+            reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<T*>(out), out_stride, width, n_rows, kind, pq, pq_dt)));
+        return rs_launch_result();
+    }
     RS_DISPATCH_DTYPE(dt, T, (activation_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
         reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<T*>(out), out_stride, width, n, kind, pq, pq_dt)));
     return rs_launch_result();

@@ -367,27 +367,44 @@ __global__ void __launch_bounds__(256) talking_combine_kernel(MmaParams p) {
     const int* wk = p.work + 5 * (size_t)blockIdx.x;
     const int s = wk[0], q0 = wk[1], part = wk[2], parts = wk[3], row_base = wk[4];
     if (part != 0 || parts <= 1) return;
+    if (parts > 32) { if (threadIdx.x == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN); return; }     // a lane per part
     const int H = p.H, dv = p.dv;
     const int t_first = p.q_start[s] + q0;
     const int nq = min(p.QT, p.q_start[s + 1] - p.q_start[s] - q0);
     if ((long)row_base + (long)parts * nq > p.partial_rows) return;           // flagged by the kernel that wrote the parts
-    for (int i = threadIdx.x; i < nq * H * dv; i += blockDim.x) {
-        const int d = i % dv, h = (i / dv) % H, qi = i / (dv * H);
-        float m = -INFINITY;
-        for (int pt = 0; pt < parts; ++pt)
-            m = fmaxf(m, p.partial[((size_t)(row_base + pt * nq + qi) * H + h) * (dv + 2) + dv]);
-        float num = 0.f, den = 0.f;
-        for (int pt = 0; pt < parts; ++pt) {
-            const float* src = p.partial + ((size_t)(row_base + pt * nq + qi) * H + h) * (dv + 2);
-            const float w = src[dv] == -INFINITY ? 0.f : expf(src[dv] - m);
-            num = fmaf(w, src[d], num);
-            den = fmaf(w, src[dv + 1], den);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    // a warp per (query, head): lane i holds part i's maximum and denominator, then the lanes share out the columns
+    for (int rowi = warp; rowi < nq * H; rowi += warps) {
+        const int qi = rowi / H, h = rowi % H;
+        const size_t pitch = (size_t)nq * H * (dv + 2);                        // from one part of the row to the next
+        const float* first = p.partial + ((size_t)(row_base + qi) * H + h) * (dv + 2);
+        float mi = -INFINITY, li = 0.f;
+        if (lane < parts) { mi = first[lane * pitch + dv]; li = first[lane * pitch + dv + 1]; }
+        float m = mi;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float wi = mi == -INFINITY ? 0.f : expf(mi - m);
+        float den = wi * li;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        float f = den > 0.f ? 1.0f / den : 0.f;
+        if (p.gate) f *= p.gate[(size_t)(t_first + qi) * H + h];
+        const size_t o0 = (size_t)(t_first + qi) * p.out_stride + (size_t)h * dv;
+        for (int d0 = 0; d0 < dv; d0 += 64) {                                   // every lane walks every round: the shuffles need them
+            const int d = d0 + 2 * lane;
+            float y0 = 0.f, y1 = 0.f;
+            for (int pt = 0; pt < parts; ++pt) {
+                const float w = __shfl_sync(0xffffffffu, wi, pt);
+                if (d < dv) {
+                    const float2 x = *reinterpret_cast<const float2*>(first + pt * pitch + d);
+                    y0 = fmaf(w, x.x, y0); y1 = fmaf(w, x.y, y1);
+                }
+            }
+            if (d >= dv) continue;
+            y0 *= f; y1 *= f;
+            if (p.out_dt == RS_F32) *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + o0 + d) = make_float2(y0, y1);
+            else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o0 + d) = __floats2bfloat162_rn(y0, y1);
         }
-        float y = den > 0.f ? num / den : 0.f;
-        if (p.gate) y *= p.gate[(size_t)(t_first + qi) * H + h];
-        const size_t o = (size_t)(t_first + qi) * p.out_stride + (size_t)h * dv + d;
-        if (p.out_dt == RS_F32) reinterpret_cast<float*>(p.out)[o] = y;
-        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
     }
 }
 

@@ -30,7 +30,7 @@ from .spec import CacheNeed, TensorNeed
 
 KEY_TILE = 32              # keys per tile of the tensor-core form
 MMA_SINGLE_Q = 4           # its query tile in a step of single tokens (the smallest it has: more CTAs fit a multiprocessor)
-FILL_CTAS = 296            # two per multiprocessor: a step with fewer tiles than half of this shares out its keys
+FILL_CTAS = 148            # one CTA per multiprocessor
 MAX_PARTS = 32
 MIN_PART_TILES = 4         # a part walks at least this many key tiles
 PARTIAL_ROWS = 4096        # (query, part) rows of partial sums the workspace holds
@@ -156,8 +156,11 @@ class TalkingAttention(Mixer):
         n = work.shape[0]
         nq = np.minimum(qt, batch.q_lens[work[:, 0]] - work[:, 1])
         parts = np.ones(n, dtype=np.int64)
-        if n < FILL_CTAS // 2:
-            share = min(MAX_PARTS, FILL_CTAS // n)
+        # single tokens: one wave of CTAs (each is mostly fixed cost); portions: up to two, which also evens out the
+        # unequal walks of a causal portion's tiles
+        fill = FILL_CTAS if single else 2 * FILL_CTAS
+        if n <= fill // 2:
+            share = min(MAX_PARTS, fill // n)
             if batch.bucketed:
                 parts[:] = share              # a captured step: the launch shape must not follow the lengths
             else:

@@ -49,6 +49,15 @@ def test_a_full_step_is_not_shared_out():
     assert (np.diff(first) <= 0).all()                                       # most keys first
 
 
+def test_one_long_portion_is_shared_out_in_two():
+    plan = make_part().build_plan(batch([2048], [2048]))
+    w = rows_of(plan)
+    heads = w[w[:, 2] == 0]
+    assert len(heads) == 128 and plan["any_parts"] == 1
+    assert (heads[heads[:, 1] >= 8 * 16 * 2, 3] == 2).all()                  # tiles with at least 8 key tiles: two parts
+    assert (heads[heads[:, 1] < 7 * 16 * 2 - 16, 3] == 1).all()              # short walks stay whole
+
+
 def test_captured_steps_keep_their_shape():
     a = make_part().build_plan(batch([1] * 8, [100 + i for i in range(8)], bucketed=True))
     b = make_part().build_plan(batch([1] * 8, [3000 + 17 * i for i in range(8)], bucketed=True))
