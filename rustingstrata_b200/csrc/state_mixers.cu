@@ -101,26 +101,38 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
     const size_t k_off = DELTA ? q_off : (size_t)h * RP;
     const size_t g_off = (size_t)h * RP;
 
+    // what this thread copies of every token: pieces tid, tid + threads, .. of the 3 RP / 4 16-byte pieces of q | k | g,
+    // and one of the CTA's values or the write strength
+    constexpr int PIECES = 3 * RP / 4, MAX_OWN = (PIECES + 63) / 64;
+    const float* own_src[MAX_OWN];
+    long own_step[MAX_OWN];
+    int own_dst[MAX_OWN];
+#pragma unroll
+    for (int e = 0; e < MAX_OWN; ++e) {
+        const int piece = tid + e * nthreads;
+        const int which = piece / (RP / 4), off = (piece % (RP / 4)) * 4;
+        own_dst[e] = piece < PIECES ? which * RP + off : -1;
+        own_step[e] = which == 0 ? p.q_stride : which == 1 ? p.k_stride : p.g_stride;
+        own_src[e] = (which == 0 ? p.q + q_off : which == 1 ? p.k + k_off : p.g + g_off) + (size_t)t0 * own_step[e] + off;
+    }
+    const bool own_v = tid < cols_cta, own_b = DELTA && tid == cols_cta;
+    const float* small_src = own_v ? p.v + (size_t)t0 * p.v_stride + (size_t)h * p.columns + min((int)blockIdx.y * cols_cta + tid, p.columns - 1)
+                                   : p.beta + (size_t)t0 * p.beta_stride + h;
+    const long small_step = own_v ? p.v_stride : p.beta_stride;
+    const int small_dst = 3 * RP + (own_v ? tid : COLS_PER_CTA);
+
     auto fetch = [&](int c) {                               // chunk c of the step's tokens into buffer c & 1
         float* dst = stage + (size_t)(c & 1) * CHUNK * ROW;
-        const int first = t0 + c * CHUNK, count = min(CHUNK, n - c * CHUNK);
-        constexpr int PER = RP / 4;                         // 16-byte pieces of a row of q, k or g
-        for (int i = tid; i < count * 3 * PER; i += nthreads) {
-            const int tt = i / (3 * PER), rest = i % (3 * PER), which = rest / PER, piece = rest % PER;
-            const size_t t = first + tt;
-            const float* src = which == 0 ? p.q + t * p.q_stride + q_off
-                             : which == 1 ? p.k + t * p.k_stride + k_off : p.g + t * p.g_stride + g_off;
-            cp_async_16(dst + tt * ROW + which * RP + piece * 4, src + piece * 4);
+        const int first = c * CHUNK, count = min(CHUNK, n - c * CHUNK);
+#pragma unroll
+        for (int e = 0; e < MAX_OWN; ++e) {
+            if (own_dst[e] < 0) continue;
+            const float* src = own_src[e] + (size_t)first * own_step[e];
+            for (int tt = 0; tt < count; ++tt) cp_async_16(dst + tt * ROW + own_dst[e], src + (size_t)tt * own_step[e]);
         }
-        for (int i = tid; i < count * (cols_cta + 1); i += nthreads) {
-            const int tt = i / (cols_cta + 1), c2 = i % (cols_cta + 1);
-            const size_t t = first + tt;
-            if (c2 < cols_cta) {
-                const int col = min((int)blockIdx.y * cols_cta + c2, p.columns - 1);
-                cp_async_4(dst + tt * ROW + 3 * RP + c2, p.v + t * p.v_stride + (size_t)h * p.columns + col);
-            } else if (DELTA) {
-                cp_async_4(dst + tt * ROW + 3 * RP + COLS_PER_CTA, p.beta + t * p.beta_stride + h);
-            }
+        if (own_v || own_b) {
+            const float* src = small_src + (size_t)first * small_step;
+            for (int tt = 0; tt < count; ++tt) cp_async_4(dst + tt * ROW + small_dst, src + (size_t)tt * small_step);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -148,6 +160,7 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
             if (part == 0 && tt < count) buf[tt * ROW + 3 * RP + COLS_PER_CTA + 1] = d;
             __syncthreads();
         }
+#pragma unroll 2
         for (int tt = 0; tt < count; ++tt) {
             const float* row = buf + tt * ROW;
             float qc[RPT], kc[RPT], gc[RPT];
