@@ -4,14 +4,15 @@
 //
 // A CTA takes up to QT neighbouring queries of one sequence, all heads, and a share of their key tiles.  Per tile of
 // KEY_TILE keys, whose boundaries are multiples of KEY_TILE counted from the sequence's first key:
-//   1. raw[g] = Q_g K_c(g)^T on mma.sync m16n8k16, a warp per head.  The float32 queries are split into two
+//   1. raw[g] = Q_g K_c(g)^T on mma.sync m16n8k16, a warp per head and half of the tile's keys.  The float32 queries are split into two
 //      bfloat16 terms (x = hi + lo, |lo| <= 2^-9 |x|) and both are multiplied, so the score carries the float32
 //      query and not its 8-bit rounding; accumulation is float32.  Scaled scores go to shared memory.
 //   2. mixed[h] = sum_g talk[h, g] raw[g] on the CUDA cores in float32: a thread owns four neighbouring keys of one
 //      query and eight output heads, so one 16-byte read of raw[g] feeds 32 multiply-adds; the causal and window
 //      masks are applied here.
 //   3. online softmax per (head, query) in float32, the running maximum and sum starting at (sink, 1); the weights,
-//      split in two bfloat16 terms like the queries, times V on the tensor cores; a warp per head.
+//      split in two bfloat16 terms like the queries, times V on the tensor cores; a warp per head (two, each with half
+//      of the value columns, when there are 8 heads or fewer).
 // K of the next tile is fetched with cp.async while steps 2 and 3 run, V of the next tile while the next step 1 runs.
 // When a tile's keys are shared out over several CTAs (few queries, many keys), each writes its unnormalised sums
 // with its maximum and denominator, and talking_combine_kernel joins them; the sink is part 0's.
@@ -77,17 +78,25 @@ __device__ __forceinline__ void locate_keys(const MmaParams& p, long long* key_a
     key_at[lane] = at;
 }
 
-// rows [KEY_TILE][G * width] of one plane of the cache into shared memory, 16 bytes per copy; rows without a key are zero
+// rows [KEY_TILE][G * width] of one plane of the cache into shared memory, 16 bytes per copy; rows without a key are zero.
+// Sixteen threads share a key's row: thread `sub` copies pieces sub, sub + 16, .. of the G * width / 8 the row has
+// (piece j is piece j % (width / 8) of kv head j / (width / 8); the pair is stepped, not divided).
 __device__ __forceinline__ void fetch_plane(const MmaParams& p, const long long* key_at, __nv_bfloat16* dst, int pitch, int width,
                                             size_t plane_off, int tid) {
+    static_assert(THREADS == KEY_TILE * 16, "sixteen threads per key");
     const int chunks = width / 8, per_key = p.G * chunks;
     const size_t head_stride = (size_t)p.page_size * p.hdp;
-    for (int i = tid; i < KEY_TILE * per_key; i += THREADS) {
-        const int kk = i / per_key, rest = i % per_key, c = rest / chunks, ch = rest % chunks;
-        __nv_bfloat16* d = dst + (size_t)kk * pitch + c * width + ch * 8;
-        const long long at = key_at[kk];
-        if (at >= 0) cp_async16(smem_addr(d), p.cache + at + plane_off + c * head_stride + ch * 8);
+    const int kk = tid >> 4, sub = tid & 15;
+    const long long at = key_at[kk];
+    __nv_bfloat16* row = dst + (size_t)kk * pitch;
+    const __nv_bfloat16* src = p.cache + (at < 0 ? 0 : at) + plane_off;
+    int c = sub / chunks, ch = sub - c * chunks;
+    for (int j = sub; j < per_key; j += 16) {
+        __nv_bfloat16* d = row + c * width + ch * 8;
+        if (at >= 0) cp_async16(smem_addr(d), src + c * head_stride + ch * 8);
         else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+        ch += 16;
+        while (ch >= chunks) { ch -= chunks; ++c; }
     }
 }
 
@@ -118,6 +127,10 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
     const int per = (kt1 - kt0 + parts - 1) / parts;
     const int t_begin = kt0 + part * per, t_end = min(kt1, t_begin + per);
     const size_t plane = (size_t)p.plane_stride;
+    const int qt_shift = QT == 16 ? 4 : QT == 8 ? 3 : 2;
+    // step 3: a warp per head; with 8 heads or fewer two warps per head, each holding half of the value columns
+    const bool pair = HPW == 1 && 2 * H <= WARPS;
+    const int col_half = pair ? (warp & 1) : 0;
 
     for (int i = tid; i < QT * H * dk; i += THREADS) {
         const int qi = i / (H * dk), c = i % (H * dk);
@@ -134,7 +147,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
     float m_run[HPW][2], l_run[HPW][2], O[HPW][DVP][2][4];
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
-        const int h = warp + WARPS * i;
+        const int h = pair ? warp >> 1 : warp + WARPS * i;
         const float sk = (p.sink && h < H) ? p.sink[h] : -INFINITY;
         m_run[i][0] = m_run[i][1] = sk;
         l_run[i][0] = l_run[i][1] = (p.sink && part == 0 && tig == 0) ? 1.f : 0.f;     // summed over the four lanes of a row at the end
@@ -161,38 +174,35 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
         __syncthreads();
         // ---- 1: raw scores, a warp per head
         if (t + 1 < t_end && tid >= THREADS - KEY_TILE) locate_keys(p, at_next, s, k0 + KEY_TILE, k_begin, k_end, lane);
-        for (int g = warp; g < H; g += WARPS) {
-            const int c = g / r;
-            float acc[4][4];
+        for (int task = warp; task < 2 * H; task += WARPS) {
+            const int g = task >> 1, half = task & 1, c = g / r;
+            float acc[2][4];
 #pragma unroll
-            for (int a = 0; a < 4; ++a)
+            for (int a = 0; a < 2; ++a)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
             const int arow = (lane & 15) < QT ? (lane & 15) : 0;
+            const int mi = lane >> 3;
+            const int key = half * 16 + (mi >> 1) * 8 + (lane & 7);
             for (int ks = 0; ks < dk / 16; ++ks) {
-                uint32_t ah[4], al[4];
+                uint32_t ah[4], al[4], b0, b1, b2, b3;
                 const size_t aoff = (size_t)arow * L.q_pitch + g * dk + ks * 16 + (lane >> 4) * 8;
                 ldmatrix_x4(smem_addr(Qhi + aoff), ah[0], ah[1], ah[2], ah[3]);
                 ldmatrix_x4(smem_addr(Qlo + aoff), al[0], al[1], al[2], al[3]);
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int mi = lane >> 3;
-                    const int key = half * 16 + (mi >> 1) * 8 + (lane & 7);
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(smem_addr(Ks + (size_t)key * L.k_pitch + c * dk + ks * 16 + (mi & 1) * 8), b0, b1, b2, b3);
-                    mma16816(acc[2 * half], ah, b0, b1);
-                    mma16816(acc[2 * half], al, b0, b1);
-                    mma16816(acc[2 * half + 1], ah, b2, b3);
-                    mma16816(acc[2 * half + 1], al, b2, b3);
-                }
+                ldmatrix_x4(smem_addr(Ks + (size_t)key * L.k_pitch + c * dk + ks * 16 + (mi & 1) * 8), b0, b1, b2, b3);
+                mma16816(acc[0], ah, b0, b1);
+                mma16816(acc[0], al, b0, b1);
+                mma16816(acc[1], ah, b2, b3);
+                mma16816(acc[1], al, b2, b3);
             }
 #pragma unroll
-            for (int nb = 0; nb < 4; ++nb) {
+            for (int nb = 0; nb < 2; ++nb) {
+                const int col = (2 * half + nb) * 8 + 2 * tig;
                 if (gid < QT)
-                    *reinterpret_cast<float2*>(Sraw + ((size_t)g * QT + gid) * SROW + nb * 8 + 2 * tig) =
+                    *reinterpret_cast<float2*>(Sraw + ((size_t)g * QT + gid) * SROW + col) =
                         make_float2(acc[nb][0] * p.scale, acc[nb][1] * p.scale);
                 if (gid + 8 < QT)
-                    *reinterpret_cast<float2*>(Sraw + ((size_t)g * QT + gid + 8) * SROW + nb * 8 + 2 * tig) =
+                    *reinterpret_cast<float2*>(Sraw + ((size_t)g * QT + gid + 8) * SROW + col) =
                         make_float2(acc[nb][2] * p.scale, acc[nb][3] * p.scale);
             }
         }
@@ -202,7 +212,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
         // ---- 2: the mix across heads and the masks
         const int items = (L.h8 / 8) * QT * 8;
         for (int i = tid; i < items; i += THREADS) {
-            const int kq = i & 7, qi = (i >> 3) % QT, hc = i / (8 * QT);
+            const int kq = i & 7, qi = (i >> 3) & (QT - 1), hc = i >> (3 + qt_shift);
             if (qi >= nq) continue;
             float acc[8][4];
 #pragma unroll
@@ -241,7 +251,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
         // ---- 3: online softmax and weighted values, a warp per head
 #pragma unroll
         for (int i = 0; i < HPW; ++i) {
-            const int h = warp + WARPS * i;
+            const int h = pair ? warp >> 1 : warp + WARPS * i;
             if (h >= H) continue;
             float sc[4][4];
 #pragma unroll
@@ -263,7 +273,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
                 mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
                 mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
                 const float m_new = fmaxf(m_run[i][e], mx[e]);
-                alpha[e] = m_new == -INFINITY ? 1.f : expf(m_run[i][e] - m_new);
+                alpha[e] = m_new == -INFINITY ? 1.f : __expf(m_run[i][e] - m_new);
                 m_run[i][e] = m_new;
             }
             float psum[2] = {0.f, 0.f};
@@ -271,7 +281,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
             for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const float v = sc[nb][b] == -INFINITY ? 0.f : expf(sc[nb][b] - m_run[i][b >> 1]);
+                    const float v = sc[nb][b] == -INFINITY ? 0.f : __expf(sc[nb][b] - m_run[i][b >> 1]);
                     sc[nb][b] = v;
                     psum[b >> 1] += v;
                 }
@@ -300,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
                 }
 #pragma unroll
                 for (int a = 0; a < DVP; ++a) {
-                    if (a * 16 >= dv) continue;
+                    if (a * 16 >= dv || (pair && (a >= DVP / 2) != (col_half == 1))) continue;
                     const int mi = lane >> 3;
                     const int key = j * 16 + (mi & 1) * 8 + (lane & 7);
                     uint32_t b0, b1, b2, b3;
@@ -320,7 +330,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
     // ---- the end: o / l * gate, or this part's sums for the combine kernel
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
-        const int h = warp + WARPS * i;
+        const int h = pair ? warp >> 1 : warp + WARPS * i;
         if (h >= H) continue;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
@@ -340,7 +350,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
 #pragma unroll
                     for (int b = 0; b < 2; ++b) {
                         const int d = a * 16 + b * 8 + 2 * tig;
-                        if (d >= dv) continue;
+                        if (d >= dv || (pair && (a >= DVP / 2) != (col_half == 1))) continue;
                         const float y0 = O[i][a][b][2 * e] * f, y1 = O[i][a][b][2 * e + 1] * f;
                         if (p.out_dt == RS_F32) *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + o + d) = make_float2(y0, y1);
                         else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o + d) = __floats2bfloat162_rn(y0, y1);
@@ -354,9 +364,10 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
 #pragma unroll
                     for (int b = 0; b < 2; ++b) {
                         const int d = a * 16 + b * 8 + 2 * tig;
-                        if (d < dv) *reinterpret_cast<float2*>(dst + d) = make_float2(O[i][a][b][2 * e], O[i][a][b][2 * e + 1]);
+                        if (d < dv && !(pair && (a >= DVP / 2) != (col_half == 1)))
+                            *reinterpret_cast<float2*>(dst + d) = make_float2(O[i][a][b][2 * e], O[i][a][b][2 * e + 1]);
                     }
-                if (tig == 0) { dst[dv] = m_run[i][e]; dst[dv + 1] = l_run[i][e]; }
+                if (tig == 0 && col_half == 0) { dst[dv] = m_run[i][e]; dst[dv + 1] = l_run[i][e]; }
             }
         }
     }
