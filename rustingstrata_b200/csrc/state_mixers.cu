@@ -22,10 +22,10 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
 // ------------------------------------------------------------------------------------------------ the recurrence
-// A column of a head's state belongs to 8 neighbouring lanes; each keeps RPT neighbouring rows of it in registers, so
-// a head has up to 8 * RPT rows.  A warp walks 4 columns, a CTA 32.  Sums over rows are three shuffles inside the 8
-// lanes: no shared memory and no barrier in the token loop, and an order of additions that depends on nothing but
-// the head's shape.  In a request's slot a head's state is stored column by column ([column][padded rows]), so the
+// A column of a head's state belongs to RL = 8 neighbouring lanes; each lane keeps RPT rows of it in registers, so a head
+// has RL * RPT rows.  A warp walks 32 / RL columns, a CTA 8, 16 or 32.  Sums over rows are
+// shuffles inside the RL lanes: no shared memory and no barrier in the token loop, and an order of additions that
+// depends on nothing but the head's shape and RL.  In a request's slot a head's state is stored column by column ([column][padded rows]), so the
 // loads and stores at both ends of a step are whole 16-byte runs.
 constexpr int ROW_LANES = 8;
 constexpr int COLS_PER_CTA = 32;
@@ -42,20 +42,20 @@ struct RecurrenceParams {
     int heads, group, columns;              // group: state heads per q/k head (delta rule)
 };
 
+template <int RL>
 __device__ __forceinline__ float sum_row_lanes(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
+#pragma unroll
+    for (int o = 1; o < RL; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 
-// Lane rl of a column keeps rows 32 i + 4 rl .. + 3 for i < RPT / 4: the eight lanes of a column read 128 neighbouring
-// bytes at a time, from shared memory without bank conflicts and from the state in whole lines.
-template <int RPT>
+// Lane rl of a column keeps rows 4 RL i + 4 rl .. + 3 for i < RPT / 4: the lanes of a column read neighbouring bytes,
+// from shared memory without bank conflicts and from the state in whole lines.
+template <int RPT, int RL>
 __device__ __forceinline__ void load_rows(const float* p, float* r) {
 #pragma unroll
     for (int m = 0; m < RPT; m += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(p + m * ROW_LANES);
+        const float4 a = *reinterpret_cast<const float4*>(p + m * RL);
         r[m] = a.x; r[m + 1] = a.y; r[m + 2] = a.z; r[m + 3] = a.w;
     }
 }
@@ -65,9 +65,9 @@ __device__ __forceinline__ void load_rows(const float* p, float* r) {
 // itself waits for nothing but its own arithmetic.  For the delta rule both sums over rows of a token are taken from
 // the decayed state S' = diag(g) S in one round of shuffles: with r = S'^T k and a = S'^T q, u = beta (v - r) and the
 // read-out of S' + k u^T is a + u (k . q).
-template <int RPT> struct RecurrenceStage {
-    static constexpr int RP = RPT * ROW_LANES;
-    static constexpr int CHUNK = RPT <= 16 ? 16 : 8;                  // tokens per buffer
+template <int RP_> struct RecurrenceStage {
+    static constexpr int RP = RP_;
+    static constexpr int CHUNK = RP_ <= 128 ? 16 : 8;                 // tokens per buffer
     static constexpr int ROW = 3 * RP + COLS_PER_CTA + 4;              // q | k | g | v of the CTA's columns | beta, pad
     static constexpr size_t BYTES = 2ull * CHUNK * ROW * sizeof(float);
 };
@@ -79,16 +79,16 @@ __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int RPT, bool DELTA>
+template <int RPT, bool DELTA, int RL>
 __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams p) {
-    using St = RecurrenceStage<RPT>;
+    using St = RecurrenceStage<RPT * RL>;
     constexpr int RP = St::RP, CHUNK = St::CHUNK, ROW = St::ROW;
     extern __shared__ __align__(16) float stage[];         // [2][CHUNK][ROW]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int rl = lane & 7, cl = lane >> 3;
+    const int rl = lane & (RL - 1), cl = lane / RL;
     const int s = blockIdx.x / p.heads, h = blockIdx.x % p.heads;
-    const int nthreads = blockDim.x, cols_cta = blockDim.x / ROW_LANES;      // a CTA walks 8, 16 or 32 columns
-    const int jl = warp * 4 + cl;                           // column within the CTA
+    const int nthreads = blockDim.x, cols_cta = blockDim.x / RL;             // a CTA walks 2 to 32 columns
+    const int jl = warp * (32 / RL) + cl;                   // column within the CTA
     const int j = blockIdx.y * cols_cta + jl;
     const bool live = j < p.columns;
     const int jc = live ? j : p.columns - 1;              // lanes beyond the last column walk it too and store nothing
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
     const int n = t1 - t0;
     float* sp = p.state + (size_t)p.slots[s] * p.state_stride + ((size_t)h * p.columns + jc) * RP + rl * 4;
     float S[RPT];
-    load_rows<RPT>(sp, S);
+    load_rows<RPT, RL>(sp, S);
     const size_t q_off = (size_t)(DELTA ? h / p.group : h) * RP;
     const size_t k_off = DELTA ? q_off : (size_t)h * RP;
     const size_t g_off = (size_t)h * RP;
@@ -164,9 +164,9 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
         for (int tt = 0; tt < count; ++tt) {
             const float* row = buf + tt * ROW;
             float qc[RPT], kc[RPT], gc[RPT];
-            load_rows<RPT>(row + rl * 4, qc);
-            load_rows<RPT>(row + RP + rl * 4, kc);
-            load_rows<RPT>(row + 2 * RP + rl * 4, gc);
+            load_rows<RPT, RL>(row + rl * 4, qc);
+            load_rows<RPT, RL>(row + RP + rl * 4, kc);
+            load_rows<RPT, RL>(row + 2 * RP + rl * 4, gc);
             const float vc = row[3 * RP + jl];
             float acc;
             if (DELTA) {
@@ -180,8 +180,8 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
                 }
                 float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
                 float a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
-                r = sum_row_lanes(r);
-                a = sum_row_lanes(a);
+                r = sum_row_lanes<RL>(r);
+                a = sum_row_lanes<RL>(a);
                 const float u = bc * (vc - r);
 #pragma unroll
                 for (int m = 0; m < RPT; ++m) S[m] = fmaf(kc[m], u, S[m]);
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
                 float a4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int m = 0; m < RPT; ++m) { S[m] = fmaf(gc[m], S[m], kc[m] * vc); a4[m & 3] = fmaf(S[m], qc[m], a4[m & 3]); }
-                acc = sum_row_lanes((a4[0] + a4[1]) + (a4[2] + a4[3]));
+                acc = sum_row_lanes<RL>((a4[0] + a4[1]) + (a4[2] + a4[3]));
             }
             if (rl == 0 && live) p.out[(size_t)(t0 + c * CHUNK + tt) * p.out_stride + (size_t)h * p.columns + j] = acc;
         }
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(RecurrenceParams 
     if (live) {
 #pragma unroll
         for (int m = 0; m < RPT; m += 4)
-            *reinterpret_cast<float4*>(sp + m * ROW_LANES) = make_float4(S[m], S[m + 1], S[m + 2], S[m + 3]);
+            *reinterpret_cast<float4*>(sp + m * RL) = make_float4(S[m], S[m + 1], S[m + 2], S[m + 3]);
     }
 }
 
@@ -411,34 +411,34 @@ RS_EXPORT int rs_state_recurrence(const float* q, long q_stride, const float* k,
     if (n_seqs <= 0) return 0;
     RecurrenceParams p{q, q_stride, k, k_stride, g, g_stride, beta, beta_stride, v, v_stride, out, out_stride, state, state_stride,
                        q_start, slots, heads, group < 1 ? 1 : group, columns};
-    // narrower CTAs when the step has few (sequence, head) pairs: the walk is a chain of dependent steps, so its time is
-    // that of one CTA, and more of them only cost reads of q, k and g that the second-level cache serves
+    // Narrower CTAs while the step has fewer than two per multiprocessor: the walk is a chain of dependent steps, so its
+    // time is that of one CTA, and more of them only cost reads of q, k and g that the second-level cache serves.  (A
+    // column over 16 or 32 lanes instead of 8 shortens a lane's sums but adds rounds of shuffles: measured, no faster.)
+    const int rl = ROW_LANES;
     int cols_cta = COLS_PER_CTA;
     while (cols_cta > 8 && (long)n_seqs * heads * ((columns + cols_cta - 1) / cols_cta) < 2 * 148) cols_cta >>= 1;
     const dim3 grid(n_seqs * heads, (columns + cols_cta - 1) / cols_cta);
-    const int threads = cols_cta * ROW_LANES;
+    const int threads = cols_cta * rl;
     static bool sized = false;          // once: the attribute is a property of the function, not of a launch
-#define RS_REC_SIZE(RPT)                                                                                                        \
-    cudaFuncSetAttribute(state_recurrence_kernel<RPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
-                         (int)RecurrenceStage<RPT>::BYTES);                                                                     \
-    cudaFuncSetAttribute(state_recurrence_kernel<RPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,                     \
-                         (int)RecurrenceStage<RPT>::BYTES);
+#define RS_REC_SIZE(RPT, RL)                                                                                                    \
+    cudaFuncSetAttribute(state_recurrence_kernel<RPT, true, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                         (int)RecurrenceStage<RPT * RL>::BYTES);                                                                \
+    cudaFuncSetAttribute(state_recurrence_kernel<RPT, false, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
+                         (int)RecurrenceStage<RPT * RL>::BYTES);
     if (!sized) {
-        RS_REC_SIZE(4) RS_REC_SIZE(8) RS_REC_SIZE(16) RS_REC_SIZE(32)
+        RS_REC_SIZE(4, 8) RS_REC_SIZE(8, 8) RS_REC_SIZE(16, 8) RS_REC_SIZE(32, 8)
         sized = true;
     }
 #undef RS_REC_SIZE
-#define RS_REC(RPT)                                                                                                    \
-    case RPT * ROW_LANES:                                                                                              \
-        if (delta) state_recurrence_kernel<RPT, true><<<grid, threads, RecurrenceStage<RPT>::BYTES, stream>>>(p);      \
-        else state_recurrence_kernel<RPT, false><<<grid, threads, RecurrenceStage<RPT>::BYTES, stream>>>(p);           \
-        break;
-    switch (rows_pad) {
-        RS_REC(4) RS_REC(8) RS_REC(16) RS_REC(32)
-        default: return (int)cudaErrorInvalidValue;
+#define RS_REC(RPT, RL)                                                                                                         \
+    if (rows_pad == RPT * RL && rl == RL) {                                                                                     \
+        if (delta) state_recurrence_kernel<RPT, true, RL><<<grid, threads, RecurrenceStage<RPT * RL>::BYTES, stream>>>(p);      \
+        else state_recurrence_kernel<RPT, false, RL><<<grid, threads, RecurrenceStage<RPT * RL>::BYTES, stream>>>(p);           \
+        return rs_launch_result();                                                                                              \
     }
+    RS_REC(4, 8) RS_REC(8, 8) RS_REC(16, 8) RS_REC(32, 8)
 #undef RS_REC
-    return rs_launch_result();
+    return (int)cudaErrorInvalidValue;
 }
 
 RS_EXPORT int rs_hgrn2_prep(const float* proj, long proj_stride, const void* f_bias, int fb_dt, const void* lower, int lo_dt, float* q,
