@@ -61,6 +61,13 @@ __host__ __device__ inline Layout make_layout(int H, int G, int dk, int dv, int 
     return L;
 }
 
+constexpr float LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
     hi = __float2bfloat16_rn(x);
     lo = __float2bfloat16_rn(x - __bfloat162float(hi));
@@ -128,6 +135,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
     const int t_begin = kt0 + part * per, t_end = min(kt1, t_begin + per);
     const size_t plane = (size_t)p.plane_stride;
     const int qt_shift = QT == 16 ? 4 : QT == 8 ? 3 : 2;
+    const uint32_t q_hi_addr = smem_addr(Qhi), q_lo_addr = smem_addr(Qlo), ks_addr = smem_addr(Ks), vs_addr = smem_addr(Vs);
     // step 3: a warp per head; with 8 heads or fewer two warps per head, each holding half of the value columns
     const bool pair = HPW == 1 && 2 * H <= WARPS;
     const int col_half = pair ? (warp & 1) : 0;
@@ -184,12 +192,14 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
             const int arow = (lane & 15) < QT ? (lane & 15) : 0;
             const int mi = lane >> 3;
             const int key = half * 16 + (mi >> 1) * 8 + (lane & 7);
-            for (int ks = 0; ks < dk / 16; ++ks) {
+            const uint32_t aoff = (uint32_t)(arow * L.q_pitch + g * dk + (lane >> 4) * 8) * 2u;
+            uint32_t a_hi = q_hi_addr + aoff, a_lo = q_lo_addr + aoff;
+            uint32_t b_at = ks_addr + (uint32_t)(key * L.k_pitch + c * dk + (mi & 1) * 8) * 2u;
+            for (int ks = 0; ks < dk / 16; ++ks, a_hi += 32u, a_lo += 32u, b_at += 32u) {      // 16 coordinates = 32 bytes a step
                 uint32_t ah[4], al[4], b0, b1, b2, b3;
-                const size_t aoff = (size_t)arow * L.q_pitch + g * dk + ks * 16 + (lane >> 4) * 8;
-                ldmatrix_x4(smem_addr(Qhi + aoff), ah[0], ah[1], ah[2], ah[3]);
-                ldmatrix_x4(smem_addr(Qlo + aoff), al[0], al[1], al[2], al[3]);
-                ldmatrix_x4(smem_addr(Ks + (size_t)key * L.k_pitch + c * dk + ks * 16 + (mi & 1) * 8), b0, b1, b2, b3);
+                ldmatrix_x4(a_hi, ah[0], ah[1], ah[2], ah[3]);
+                ldmatrix_x4(a_lo, al[0], al[1], al[2], al[3]);
+                ldmatrix_x4(b_at, b0, b1, b2, b3);
                 mma16816(acc[0], ah, b0, b1);
                 mma16816(acc[0], al, b0, b1);
                 mma16816(acc[1], ah, b2, b3);
@@ -267,7 +277,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
                 mx[0] = fmaxf(mx[0], fmaxf(sc[nb][0], sc[nb][1]));
                 mx[1] = fmaxf(mx[1], fmaxf(sc[nb][2], sc[nb][3]));
             }
-            float alpha[2];
+            float alpha[2], neg_m[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
@@ -275,13 +285,14 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
                 const float m_new = fmaxf(m_run[i][e], mx[e]);
                 alpha[e] = m_new == -INFINITY ? 1.f : __expf(m_run[i][e] - m_new);
                 m_run[i][e] = m_new;
+                neg_m[e] = m_new == -INFINITY ? 0.f : -m_new * LOG2E;         // exp(s - m) = 2^(s log2 e - m log2 e); 2^-inf = 0
             }
             float psum[2] = {0.f, 0.f};
 #pragma unroll
             for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const float v = sc[nb][b] == -INFINITY ? 0.f : __expf(sc[nb][b] - m_run[i][b >> 1]);
+                    const float v = ex2_approx(fmaf(sc[nb][b], LOG2E, neg_m[b >> 1]));
                     sc[nb][b] = v;
                     psum[b >> 1] += v;
                 }
@@ -301,20 +312,17 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {             // a0: row gid, keys 2 tig..; a1: row gid + 8; a2, a3: the next 8 keys
                     const float x0 = sc[2 * j + (e >> 1)][(e & 1) * 2], x1 = sc[2 * j + (e >> 1)][(e & 1) * 2 + 1];
-                    __nv_bfloat16 h0, l0, h1, l1;
-                    split_bf16(x0, h0, l0);
-                    split_bf16(x1, h1, l1);
-                    __nv_bfloat162 hh = __halves2bfloat162(h0, h1), ll = __halves2bfloat162(l0, l1);
-                    ah[e] = *reinterpret_cast<uint32_t*>(&hh);
-                    al[e] = *reinterpret_cast<uint32_t*>(&ll);
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+                    const __nv_bfloat162 ll = __floats2bfloat162_rn(x0 - __low2float(hh), x1 - __high2float(hh));
+                    ah[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                    al[e] = *reinterpret_cast<const uint32_t*>(&ll);
                 }
+                const uint32_t v_at = vs_addr + (uint32_t)((j * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * L.v_pitch + vcol + (lane >> 4) * 8) * 2u;
 #pragma unroll
                 for (int a = 0; a < DVP; ++a) {
                     if (a * 16 >= dv || (pair && (a >= DVP / 2) != (col_half == 1))) continue;
-                    const int mi = lane >> 3;
-                    const int key = j * 16 + (mi & 1) * 8 + (lane & 7);
                     uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4_trans(smem_addr(Vs + (size_t)key * L.v_pitch + vcol + a * 16 + (mi >> 1) * 8), b0, b1, b2, b3);
+                    ldmatrix_x4_trans(v_at + a * 32u, b0, b1, b2, b3);
                     mma16816(O[i][a][0], ah, b0, b1);
                     mma16816(O[i][a][0], al, b0, b1);
                     mma16816(O[i][a][1], ah, b2, b3);
