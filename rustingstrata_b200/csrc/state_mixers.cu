@@ -22,8 +22,8 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
 // ------------------------------------------------------------------------------------------------ the recurrence
-// A column of a head's state belongs to RL = 8 neighbouring lanes; each lane keeps RPT rows of it in registers, so a head
-// has RL * RPT rows.  A warp walks 32 / RL columns, a CTA 8, 16 or 32.  Sums over rows are
+// A column of a head's state belongs to RL = 8 (16 in small steps) neighbouring lanes; each lane keeps RPT rows of it in
+// registers, so a head has RL * RPT rows.  A warp walks 32 / RL columns, a CTA 8, 16 or 32.  Sums over rows are
 // shuffles inside the RL lanes: no shared memory and no barrier in the token loop, and an order of additions that
 // depends on nothing but the head's shape and RL.  In a request's slot a head's state is stored column by column ([column][padded rows]), so the
 // loads and stores at both ends of a step are whole 16-byte runs.
@@ -412,10 +412,13 @@ RS_EXPORT int rs_state_recurrence(const float* q, long q_stride, const float* k,
     RecurrenceParams p{q, q_stride, k, k_stride, g, g_stride, beta, beta_stride, v, v_stride, out, out_stride, state, state_stride,
                        q_start, slots, heads, group < 1 ? 1 : group, columns};
     // Narrower CTAs while the step has fewer than two per multiprocessor: the walk is a chain of dependent steps, so its
-    // time is that of one CTA, and more of them only cost reads of q, k and g that the second-level cache serves.  (A
-    // column over 16 or 32 lanes instead of 8 shortens a lane's sums but adds rounds of shuffles: measured, no faster.)
-    const int rl = ROW_LANES;
-    int cols_cta = COLS_PER_CTA;
+    // time is that of one CTA, and more of them only cost reads of q, k and g that the second-level cache serves.  A
+    // small step (no more than a warp per scheduler even so) puts a column over 16 lanes instead of 8: half the
+    // instructions per warp and token for one more round of shuffles.  (Over 32 lanes: measured, no faster.)
+    const long narrow_warps = (long)n_seqs * heads * ((columns + 3) / 4);
+    const bool wide = rows_pad >= 64 && narrow_warps * 2 <= 148L * 4;
+    const int rl = wide ? 16 : ROW_LANES;
+    int cols_cta = wide ? 16 : COLS_PER_CTA;
     while (cols_cta > 8 && (long)n_seqs * heads * ((columns + cols_cta - 1) / cols_cta) < 2 * 148) cols_cta >>= 1;
     const dim3 grid(n_seqs * heads, (columns + cols_cta - 1) / cols_cta);
     const int threads = cols_cta * rl;
@@ -427,6 +430,7 @@ RS_EXPORT int rs_state_recurrence(const float* q, long q_stride, const float* k,
                          (int)RecurrenceStage<RPT * RL>::BYTES);
     if (!sized) {
         RS_REC_SIZE(4, 8) RS_REC_SIZE(8, 8) RS_REC_SIZE(16, 8) RS_REC_SIZE(32, 8)
+        RS_REC_SIZE(4, 16) RS_REC_SIZE(8, 16) RS_REC_SIZE(16, 16)
         sized = true;
     }
 #undef RS_REC_SIZE
@@ -436,7 +440,7 @@ RS_EXPORT int rs_state_recurrence(const float* q, long q_stride, const float* k,
         else state_recurrence_kernel<RPT, false, RL><<<grid, threads, RecurrenceStage<RPT * RL>::BYTES, stream>>>(p);           \
         return rs_launch_result();                                                                                              \
     }
-    RS_REC(4, 8) RS_REC(8, 8) RS_REC(16, 8) RS_REC(32, 8)
+    RS_REC(4, 8) RS_REC(8, 8) RS_REC(16, 8) RS_REC(32, 8) RS_REC(4, 16) RS_REC(8, 16) RS_REC(16, 16)
 #undef RS_REC
     return (int)cudaErrorInvalidValue;
 }

@@ -1,5 +1,5 @@
 """The state-matrix recurrence kernel against a float64 walk: both forms, every row padding, CTAs of 8, 16 and 32
-columns (the launcher picks by the step's size), column counts that fill no CTA, sequences whose lengths sit on and
+columns and columns over 8 or 16 lanes (the launcher picks by the step's size), column counts that fill no CTA, sequences whose lengths sit on and
 around the borders of the staged chunks, states that come from an earlier step, slots in any order."""
 import numpy as np
 import pytest
@@ -31,6 +31,7 @@ CASES = [
     (256, 24, 2, 1, [7, 8, 9, 17]),                     # 32 rows a lane: chunks of 8 tokens
     (32, 64, 4, 2, [3] * 38 + [19, 1]),                 # 40 x 4 x 2 CTAs of 32 columns
     (64, 64, 4, 4, [5] * 20 + [18]),                    # 21 x 4 x 4: CTAs of 16 columns
+    (128, 40, 2, 1, [17, 5]),                           # a small step: a column over 16 lanes, 8 rows a lane
 ]
 
 
