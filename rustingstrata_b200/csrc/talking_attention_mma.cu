@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
 }
 
 // joins the parts of every tile whose keys were shared out: a CTA per work item, those of part 0 do the work
-__global__ void __launch_bounds__(256) talking_combine_kernel(MmaParams p) {
+__global__ void __launch_bounds__(1024) talking_combine_kernel(MmaParams p) {
     const int* wk = p.work + 5 * (size_t)blockIdx.x;
     const int s = wk[0], q0 = wk[1], part = wk[2], parts = wk[3], row_base = wk[4];
     if (part != 0 || parts <= 1) return;
@@ -475,7 +475,8 @@ RS_EXPORT int rs_talking_attention_mma(const float* q, long q_stride, const floa
     else rc = launch<1, 8>(p, n_work, smem, stream);
     if (rc) return rc;
     if (any_parts) {
-        talking_combine_kernel<<<n_work, 256, 0, stream>>>(p);
+        // a warp's rows are chains of dependent loads: many warps, few rows each
+        talking_combine_kernel<<<n_work, QT * H >= 64 ? 1024 : 256, 0, stream>>>(p);
         return rs_launch_result();
     }
     return 0;
