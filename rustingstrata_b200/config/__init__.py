@@ -2,6 +2,7 @@ from .model_config import ConfigError, Qwen3Config, read_config_json, FULL_ATTEN
 from .lokinex_config import LokinexConfig
 from .tabedra_config import TabedraConfig
 from .kupelix_config import KupelixConfig
+from .kozasun_config import KozasunConfig
 from .engine_config import EngineConfig
 from .registry import (Architecture, register_architecture, unregister_architecture, registered_architectures,
                        resolve_architecture, load_model_config)

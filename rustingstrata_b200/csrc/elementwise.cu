@@ -361,26 +361,28 @@ RS_EXPORT int rs_qk_norm_rope_kv(void* qkv, int dt, long row_stride, int n_q, in
     return 0;
 }
 
-// --------------------------------------------------------------------------- SiLU(gate) * up
-// in: [rows, 2*I] with gate in columns [0, I) and up in [I, 2I); out: [rows, I].
+// --------------------------------------------------------------------------- act(gate) * up
+// in: [rows, 2*I] with gate in columns [0, I) and up in [I, 2I); out: [rows, I].  act: 0 SiLU, 1 the tanh form of GELU,
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))); float32 arithmetic.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, long in_stride, T* __restrict__ out, long out_stride,
-                                int rows, int I) {
+                                int rows, int I, int act) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)rows * I) return;
     const int r = (int)(idx / I), c = (int)(idx % I);
     const float g = to_f32<T>(in[(size_t)r * in_stride + c]);
     const float u = to_f32<T>(in[(size_t)r * in_stride + I + c]);
-    out[(size_t)r * out_stride + c] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    const float a = act == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+    out[(size_t)r * out_stride + c] = from_f32<T>(a * u);
 }
 
-RS_EXPORT int rs_silu_mul(const void* in, long in_stride, void* out, long out_stride, int dt, int rows, int I,
+RS_EXPORT int rs_silu_mul(const void* in, long in_stride, void* out, long out_stride, int dt, int rows, int I, int act,
                           void* stream) {
     if (rows <= 0) return 0;
     const long n = (long)rows * I;
     RS_DISPATCH_DTYPE(dt, T,
         silu_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const T*)in, in_stride,
-                                                                                       (T*)out, out_stride, rows, I));
+                                                                                       (T*)out, out_stride, rows, I, act));
     return rs_launch_result();
 }
 

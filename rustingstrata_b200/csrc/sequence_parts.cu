@@ -640,6 +640,29 @@ RS_EXPORT int rs_latent_kv_write(const float* dkv, long dkv_stride, const void* 
     return rs_launch_result();
 }
 
+// --------------------------------------------------------------------------- a gate per head
+// a[t, h * dv + d] *= sigmoid(g[t, h]) in place; g float32 (pre-activations), the sigmoid in float32
+__global__ void head_sigmoid_gate_kernel(void* __restrict__ a, int dt, long a_stride, const float* __restrict__ g, long g_stride,
+                                         int heads, int dv, long n) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int w = heads * dv;
+    const long t = idx / w;
+    const int c = (int)(idx % w);
+    const float z = g[t * g_stride + c / dv];
+    const size_t at = (size_t)t * a_stride + c;
+    store_any(a, dt, at, load_any(a, dt, at) * (1.0f / (1.0f + expf(-z))));
+}
+
+RS_EXPORT int rs_head_sigmoid_gate(void* a, int dt, long a_stride, const float* g, long g_stride, int heads, int dv,
+                                   int n_tokens, void* stream) {
+    const long n = (long)n_tokens * heads * dv;
+    if (n <= 0) return 0;
+    head_sigmoid_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, dt, a_stride, g, g_stride, heads,
+                                                                                           dv, n);
+    return rs_launch_result();
+}
+
 // --------------------------------------------------------------------------- activations
 // out[r, c] = relu(in[r, c])^2
 __global__ void relu_squared_kernel(const void* __restrict__ in, int dt, long in_stride, void* __restrict__ out,

@@ -3,9 +3,10 @@
 //       gated write   S = diag(g) S + w v^T,                                    o = S^T q      (HGRN2: g = f, w = 1 - f)
 //       delta rule    S = diag(g) S;  u = beta (v - S^T k);  S = S + k u^T;     o = S^T q      (decay per key channel)
 //   * hgrn2_prep: q = silu(.), forget gate with a lower bound, both laid out in padded rows;
+//   * retention_prep: q and k rotated by position (halves of the rotated prefix paired), k scaled, in padded rows;
 //   * delta_prep: short convolution over time + silu on q, k, v; unit-length q and k; decay and write strength;
 //   * conv_tail_update: a request's last taps - 1 projected rows after the step;
-//   * head_norm_gate: every head's read-out divided by its root mean square, times a weight and a sigmoid gate;
+//   * head_norm_gate: every head's read-out divided by its root mean square, times a weight and a sigmoid or SiLU gate;
 //   * activation: elementwise xIELU / tanh-GELU;  scale_rows: float32 rows times one number.
 // Gates, decays, norms and the state are float32 whatever the engine's element type.
 #include "common.cuh"
@@ -226,6 +227,39 @@ __global__ void hgrn2_prep_kernel(const float* proj, long proj_stride, const voi
     q[idx] = qv; g[idx] = gv; w[idx] = wv;
 }
 
+// proj [T, q (heads * dim) | k (heads * dim) | ...] float32: the first n_rot coordinates of every q and k head turned by
+// the token's position, coordinate i < n_rot / 2 together with i + n_rot / 2 (cos_sin [positions, cos | sin]), k times
+// k_scale afterwards; rows padded to rows_pad with zeros.
+__global__ void retention_prep_kernel(const float* proj, long proj_stride, const float* cos_sin, int n_rot, int table_rows,
+                                      const int* positions, int pos_stride, float k_scale, float* q, float* k, int heads, int dim,
+                                      int rows_pad, long n, int* status) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int i = (int)(idx % rows_pad);
+    const int h = (int)((idx / rows_pad) % heads);
+    const long t = idx / ((long)rows_pad * heads);
+    float qv = 0.f, kv = 0.f;
+    if (i < dim) {
+        const float* qrow = proj + t * proj_stride + (size_t)h * dim;
+        const float* krow = qrow + (size_t)heads * dim;
+        qv = qrow[i]; kv = krow[i];
+        if (i < n_rot) {
+            const int half = n_rot >> 1;
+            const int pos = positions[t * pos_stride];
+            if (pos >= table_rows && i == 0) atomicOr(status, RS_STATUS_BAD_PLAN);                // a position the table does not hold
+            const float* cs = cos_sin + (size_t)(pos < table_rows ? pos : table_rows - 1) * n_rot;
+            const int a = i < half ? i : i - half;
+            const float c = cs[a], sn = cs[half + a];
+            const int j = i < half ? i + half : i - half;
+            const float sg = i < half ? -sn : sn;
+            qv = fmaf(qv, c, qrow[j] * sg);
+            kv = fmaf(kv, c, krow[j] * sg);
+        }
+        kv *= k_scale;
+    }
+    q[idx] = qv; k[idx] = kv;
+}
+
 // ------------------------------------------------------------------------------------------------ delta rule: inputs
 constexpr int MAX_PER_LANE = 8;          // heads of up to 256 channels
 
@@ -334,7 +368,7 @@ __global__ void conv_tail_update_kernel(const float* proj, long proj_stride, flo
 // A warp per (token, head): o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) (weight and gate optional).
 __global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* o, long o_stride, const void* weight, int w_dt, const float* gate,
                                                             long gate_stride, void* out, int out_dt, long out_stride, int heads, int vdim,
-                                                            float eps, int n_tokens) {
+                                                            float eps, int n_tokens, int gate_silu) {
     const int lane = threadIdx.x & 31;
     const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (wid >= (long)n_tokens * heads) return;
@@ -347,7 +381,10 @@ __global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* o, lon
     for (int d = lane; d < vdim; d += 32) {
         float y = row[d] * r;
         if (weight) y *= load_any(weight, w_dt, d);
-        if (gate) y *= sigmoid_f(gate[(size_t)t * gate_stride + (size_t)h * vdim + d]);
+        if (gate) {
+            const float z = gate[(size_t)t * gate_stride + (size_t)h * vdim + d];
+            y *= gate_silu ? silu_f(z) : sigmoid_f(z);
+        }
         store_any(out, out_dt, (size_t)t * out_stride + (size_t)h * vdim + d, y);
     }
 }
@@ -476,11 +513,22 @@ RS_EXPORT int rs_delta_prep(const float* proj, long proj_stride, const void* con
 
 RS_EXPORT int rs_head_norm_gate(const float* o, long o_stride, const void* weight, int w_dt, const float* gate, long gate_stride,
                                 void* out, int out_dt, long out_stride, int heads, int vdim, float eps, int n_tokens,
-                                cudaStream_t stream) {
+                                int gate_silu, cudaStream_t stream) {
     const long warps = (long)n_tokens * heads;
     if (warps <= 0) return 0;
     head_norm_gate_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(o, o_stride, weight, w_dt, gate, gate_stride, out, out_dt,
-                                                                          out_stride, heads, vdim, eps, n_tokens);
+                                                                          out_stride, heads, vdim, eps, n_tokens, gate_silu);
+    return rs_launch_result();
+}
+
+RS_EXPORT int rs_retention_prep(const float* proj, long proj_stride, const float* cos_sin, int n_rot, int table_rows,
+                                const int* positions, int pos_stride, float k_scale, float* q, float* k, int heads, int dim,
+                                int rows_pad, int n_tokens, int* status, cudaStream_t stream) {
+    const long n = (long)n_tokens * heads * rows_pad;
+    if (n <= 0) return 0;
+    if ((n_rot & 1) || n_rot > dim || (n_rot > 0 && (!cos_sin || table_rows < 1))) return (int)cudaErrorInvalidValue;
+    retention_prep_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(proj, proj_stride, cos_sin, n_rot, table_rows, positions,
+                                                                          pos_stride, k_scale, q, k, heads, dim, rows_pad, n, status);
     return rs_launch_result();
 }
 

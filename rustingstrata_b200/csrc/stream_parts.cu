@@ -4,7 +4,8 @@
 //   * stream_layernorm: layer norm (weight and bias) of a weighted sum of the residual streams of a token;
 //   * stream_update: all streams at once from the old ones, x_t <- sum_s mix[s, t] x_s + out[t] y, and in the same
 //     pass the layer norm of the next reader's weighted sum;
-//   * router_topk: softmax over expert logits, choice by score + correction, weights from the uncorrected scores
+//   * router_topk: softmax or sigmoid over expert logits, choice by score + correction (within the best groups of
+//     experts, if they form groups), weights from the uncorrected scores
 //     of the chosen experts divided by their sum.
 // Everything here is float32 whatever the activation type is; a token's row is computed in an order that only the
 // row's own width fixes, never the batch.
@@ -27,6 +28,7 @@ struct EmbedSumParams {
     const int* prev_state; long state_stride;
     float* out; long out_stride; int copies; int D;
     int* status;
+    float tok_scale;                     // the token row is multiplied by it
 };
 
 __global__ void embed_sum_kernel(const EmbedSumParams p) {
@@ -55,7 +57,7 @@ __global__ void embed_sum_kernel(const EmbedSumParams p) {
     }
     float* o = p.out + (size_t)t * p.out_stride;
     for (int i = threadIdx.x; i < p.D; i += blockDim.x) {
-        float v = load_any(p.tok, p.tok_dt, (size_t)id * p.D + i);
+        float v = load_any(p.tok, p.tok_dt, (size_t)id * p.D + i) * p.tok_scale;
         if (row >= 0) v += load_any(p.bigram, p.bigram_dt, (size_t)row * p.D + i);
         if (p.pos != nullptr) v += load_any(p.pos, p.pos_dt, (size_t)place * p.D + i);
         for (int c = 0; c < p.copies; ++c) o[(size_t)c * p.D + i] = v;
@@ -163,31 +165,70 @@ __global__ void stream_update_kernel(const StreamUpdateParams p) {
                   (size_t)r * p.next.out_stride, scratch);
 }
 
-// one warp per token: scores = softmax(logits); the `top` largest of scores + correction are chosen (the lower
-// index on a tie); weights = their scores / (sum of their scores + 1e-20)
+// one warp per token: scores = softmax(logits), or sigmoid(logits) each for itself (``sigmoid``); the `top` largest of
+// scores + correction are chosen (the lower index on a tie); with ``n_groups`` > 0 the experts form that many equal
+// groups of neighbours, a group is worth the sum of its two largest scores + correction, and only experts of the
+// ``keep`` groups worth most can be chosen (the lower index on a tie); weights = the chosen experts' scores times
+// ``scale``, divided by (their sum + 1e-20) first when ``renorm`` is set
 __global__ void router_topk_kernel(const float* __restrict__ logits, long l_stride, const void* __restrict__ corr,
-                                   int corr_dt, int E, int top, int n_tokens, int* __restrict__ choice,
-                                   float* __restrict__ weight, int* status) {
+                                   int corr_dt, int E, int top, int n_tokens, int sigmoid, int n_groups, int keep, float scale,
+                                   int renorm, int* __restrict__ choice, float* __restrict__ weight, int* status) {
     extern __shared__ float sm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     const int t = blockIdx.x * wpb + warp;
     if (t >= n_tokens) return;
-    float* score = sm + (size_t)warp * 2 * E;
+    float* score = sm + (size_t)warp * (2 * E + 2 * n_groups);
     float* pick = score + E;
+    float* worth = pick + E;                 // [n_groups]
+    float* kept = worth + n_groups;          // [n_groups] 1: the group's experts can be chosen
     const float* z = logits + (size_t)t * l_stride;
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); score[e] = v; sum += v; }
-    sum = warp_sum(sum);
-    if (!(sum > 0.f) || !isfinite(sum)) { if (lane == 0) atomicOr(status, RS_STATUS_NON_FINITE); }
-    for (int e = lane; e < E; e += 32) {
-        const float s = score[e] / sum;
-        score[e] = s;
-        pick[e] = corr != nullptr ? s + load_any(corr, corr_dt, e) : s;
+    if (sigmoid) {
+        bool bad = false;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            bad |= !isfinite(v);
+            score[e] = 1.0f / (1.0f + expf(-v));
+        }
+        if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, RS_STATUS_NON_FINITE);
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - m); score[e] = v; sum += v; }
+        sum = warp_sum(sum);
+        if (!(sum > 0.f) || !isfinite(sum)) { if (lane == 0) atomicOr(status, RS_STATUS_NON_FINITE); }
+        for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
     }
+    for (int e = lane; e < E; e += 32) pick[e] = corr != nullptr ? score[e] + load_any(corr, corr_dt, e) : score[e];
     __syncwarp();
+    if (n_groups > 0) {
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;              // the group's largest and second largest
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = pick[e];
+                if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+            }
+            worth[g] = per > 1 ? a + b : a;
+            kept[g] = 0.f;
+        }
+        __syncwarp();
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY; int bi = 0x7FFFFFFF;
+            for (int g = lane; g < n_groups; g += 32) { const float v = worth[g]; if (kept[g] == 0.f && (v > best || bi == 0x7FFFFFFF)) { best = v; bi = g; } }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7FFFFFFF && (bi == 0x7FFFFFFF || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+            }
+            if (bi >= 0 && bi < n_groups && lane == 0) kept[bi] = 1.f;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) if (kept[e / per] == 0.f) pick[e] = -INFINITY;
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY; int bi = 0x7FFFFFFF;
@@ -204,9 +245,9 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long l_stri
         if (lane == 0) { choice[(size_t)t * top + k] = bi; weight[(size_t)t * top + k] = s; pick[bi] = -INFINITY; }
         __syncwarp();
     }
-    const float inv = 1.0f / (total + 1e-20f);
+    const float f = renorm ? scale / (total + 1e-20f) : scale;
     __syncwarp();
-    for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= inv;
+    for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= f;
 }
 }  // namespace
 
@@ -214,11 +255,11 @@ RS_EXPORT int rs_embed_sum(const void* tok, int tok_dt, int V, const void* bigra
                            long mul_cur, const void* pos, int pos_dt, int n_pos, const int* ids, const int* positions,
                            int pos_stride, const int* seq_of_token, const int* q_start, const int* slots, int* prev_state,
                            long state_stride, float* out, long out_stride, int copies, int D, int n_tokens, int n_seqs,
-                           int* status, void* stream) {
+                           float tok_scale, int* status, void* stream) {
     if (n_tokens <= 0) return 0;
     if (bigram != nullptr && (buckets <= 0 || prev_state == nullptr)) return (int)cudaErrorInvalidValue;
     EmbedSumParams p{tok, tok_dt, V, bigram, bigram_dt, buckets, mul_prev, mul_cur, pos, pos_dt, n_pos, ids, positions,
-                     pos_stride, seq_of_token, q_start, slots, prev_state, state_stride, out, out_stride, copies, D, status};
+                     pos_stride, seq_of_token, q_start, slots, prev_state, state_stride, out, out_stride, copies, D, status, tok_scale};
     cudaStream_t s = (cudaStream_t)stream;
     embed_sum_kernel<<<n_tokens, D >= 1024 ? 256 : 128, 0, s>>>(p);
     int e = rs_launch_result();
@@ -263,11 +304,15 @@ RS_EXPORT int rs_stream_update(float* x, long x_stride, const float* y, long y_s
 }
 
 RS_EXPORT int rs_router_topk(const float* logits, long l_stride, const void* corr, int corr_dt, int E, int top, int n_tokens,
-                             int* choice, float* weight, int* status, void* stream) {
+                             int sigmoid, int n_groups, int keep, float scale, int renorm, int* choice, float* weight, int* status,
+                             void* stream) {
     if (n_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || E > 1024) return (int)cudaErrorInvalidValue;
+    if (n_groups < 0 || (n_groups > 0 && (E % n_groups || keep < 1 || keep > n_groups || top > keep * (E / n_groups))))
+        return (int)cudaErrorInvalidValue;
     const int wpb = 4;
-    router_topk_kernel<<<(n_tokens + wpb - 1) / wpb, wpb * 32, (size_t)wpb * 2 * E * sizeof(float), (cudaStream_t)stream>>>(
-        logits, l_stride, corr, corr_dt, E, top, n_tokens, choice, weight, status);
+    router_topk_kernel<<<(n_tokens + wpb - 1) / wpb, wpb * 32, (size_t)wpb * (2 * E + 2 * n_groups) * sizeof(float),
+                         (cudaStream_t)stream>>>(
+        logits, l_stride, corr, corr_dt, E, top, n_tokens, sigmoid, n_groups, keep, scale, renorm, choice, weight, status);
     return rs_launch_result();
 }

@@ -1,10 +1,13 @@
 // Attention whose scores are mixed across heads before the softmax ("talking heads"), with a learned sink in every
 // head's denominator and a gate per head on the way out, over the paged key/value cache, for both engines:
-//   * talking_attention_prep: biases, RMS norm of every q and k head, rotation of neighbouring pairs, q to float32
-//     rows, k and v into the request's cache pages, sigmoid of the head gates;
+//   * talking_attention_prep: biases, RMS norm of every q and k head (or one norm over the whole q row and one over the
+//     whole k row, with a weight per coordinate), rotation of neighbouring pairs or of the halves of the rotated prefix,
+//     q to float32 rows, k and v into the request's cache pages, sigmoid of the head gates;
 //   * talking_attention: for a tile of queries of one sequence, key tile by key tile: raw scores of all heads,
 //     mixed[h] = sum_g talk[h, g] raw[g], online softmax per (head, query) whose running maximum and sum start at
 //     (sink, 1) instead of (-inf, 0), weighted sum of values, and at the end o / l * gate.
+// A query sees the keys up to its own position, within ``window`` keys if there is a window, and within its own block
+// of ``chunk`` positions (counted from the sequence's first) if the attention is chunked.
 // Scores, weights, the mix and the sums are float32; keys and values have the cache's element type.  Key tiles start
 // at multiples of KEY_TILE counted from the sequence's first key, so the order in which a query's keys enter its sums
 // does not depend on how the sequence was cut into steps or on what else is in the batch.
@@ -27,7 +30,9 @@ struct PrepParams {
     const float* proj; long proj_stride;      // [T, q (H * dk) | k (G * dk) | v (G * dv) | gate (H)]
     const void* bias; int bias_dt;            // [H * dk + G * dk + G * dv] or null
     const void* q_norm; const void* k_norm; int norm_dt; float eps;     // [dk] each, or null: no norm
+    int row_norm;                             // 1: one norm over the whole q row and one over the whole k row, weights [H * dk], [G * dk]
     const float* cos_sin; int n_rot; int table_rows;                     // [rows, cos(n_rot / 2) | sin(n_rot / 2)]
+    int half_pairs;                           // 0: coordinate 2i turns with 2i + 1; 1: coordinate i with i + n_rot / 2
     float* q_out; long q_stride;              // [T, H * dk]
     float* gate_out;                          // [T, H] or null
     void* cache; int cache_dt; long page_stride; long plane_stride; int num_pages, page_size, hdp;
@@ -37,14 +42,10 @@ struct PrepParams {
     int* status;
 };
 
-// A warp per (token, item): the q heads, then the k heads, then the v heads, then one item for the gates.
-__global__ void __launch_bounds__(THREADS) talking_prep_kernel(PrepParams p) {
-    const int lane = threadIdx.x & 31;
+// One (token, item): the q heads, then the k heads, then the v heads, then one item for the gates.  ``inv_q`` and
+// ``inv_k`` are the row norms' factors (row_norm only); ``turn`` is the warp's 256 floats of shared memory.
+__device__ __forceinline__ void prep_item(const PrepParams& p, int t, int item, int lane, float inv_q, float inv_k, float* turn) {
     const int kv_items = p.write_kv ? 2 * p.G : 0;
-    const int items = p.H + kv_items + (p.has_gate ? 1 : 0);
-    const long wid = (long)blockIdx.x * WARPS + (threadIdx.x >> 5);
-    if (wid >= (long)p.n_tokens * items) return;
-    const int t = (int)(wid / items), item = (int)(wid % items);
     const float* row = p.proj + (size_t)t * p.proj_stride;
     if (item == p.H + kv_items) {
         const int off = p.H * p.dk + p.G * (p.dk + p.dv);
@@ -70,25 +71,52 @@ __global__ void __launch_bounds__(THREADS) talking_prep_kernel(PrepParams p) {
     if (kind != 2) {
         const void* nw = kind == 0 ? p.q_norm : p.k_norm;
         if (nw) {
-            ss = warp_sum(ss);
-            const float r = 1.0f / sqrtf(ss / (float)width + p.eps);
+            float r;
+            int w0 = 0;
+            if (p.row_norm) {
+                r = kind == 0 ? inv_q : inv_k;
+                w0 = head * p.dk;                    // the weight has a value per coordinate of the row
+            } else {
+                ss = warp_sum(ss);
+                r = 1.0f / sqrtf(ss / (float)width + p.eps);
+            }
 #pragma unroll
             for (int m = 0; m < MAX_PER_LANE; ++m) {
                 const int d = lane + 32 * m;
-                if (d < width) x[m] = x[m] * r * load_any(nw, p.norm_dt, d);
+                if (d < width) x[m] = x[m] * r * load_any(nw, p.norm_dt, w0 + d);
             }
         }
         if (p.n_rot > 0) {
             const int half = p.n_rot >> 1;
             const int trow = pos < p.table_rows ? pos : p.table_rows - 1;
+            if (pos >= p.table_rows && lane == 0) atomicOr(p.status, RS_STATUS_BAD_PLAN);       // a position the table does not hold
             const float* cs = p.cos_sin + (size_t)trow * p.n_rot;
+            if (p.half_pairs) {
+                // coordinate i turns with i + half: the partner lies in another lane and register, so the row makes a
+                // round trip through the warp's shared memory
+                __syncwarp();
 #pragma unroll
-            for (int m = 0; m < MAX_PER_LANE; ++m) {
-                const int d = lane + 32 * m;
-                const float other = __shfl_xor_sync(0xffffffffu, x[m], 1);    // coordinate d ^ 1: the pair's other half
-                if (d < p.n_rot && d < width) {
-                    const float c = cs[d >> 1], sn = cs[half + (d >> 1)];
-                    x[m] = (d & 1) ? fmaf(x[m], c, other * sn) : fmaf(x[m], c, -other * sn);
+                for (int m = 0; m < MAX_PER_LANE; ++m) { const int d = lane + 32 * m; if (d < p.n_rot) turn[d] = x[m]; }
+                __syncwarp();
+#pragma unroll
+                for (int m = 0; m < MAX_PER_LANE; ++m) {
+                    const int d = lane + 32 * m;
+                    if (d < p.n_rot && d < width) {
+                        const int i = d < half ? d : d - half;
+                        const float c = cs[i], sn = cs[half + i];
+                        const float other = turn[d < half ? d + half : d - half];
+                        x[m] = d < half ? fmaf(x[m], c, -other * sn) : fmaf(x[m], c, other * sn);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int m = 0; m < MAX_PER_LANE; ++m) {
+                    const int d = lane + 32 * m;
+                    const float other = __shfl_xor_sync(0xffffffffu, x[m], 1);    // coordinate d ^ 1: the pair's other half
+                    if (d < p.n_rot && d < width) {
+                        const float c = cs[d >> 1], sn = cs[half + (d >> 1)];
+                        x[m] = (d & 1) ? fmaf(x[m], c, other * sn) : fmaf(x[m], c, -other * sn);
+                    }
                 }
             }
         }
@@ -111,6 +139,43 @@ __global__ void __launch_bounds__(THREADS) talking_prep_kernel(PrepParams p) {
     }
 }
 
+// A warp per (token, item).
+__global__ void __launch_bounds__(THREADS) talking_prep_kernel(PrepParams p) {
+    __shared__ float turn[WARPS][32 * MAX_PER_LANE];
+    const int items = p.H + (p.write_kv ? 2 * p.G : 0) + (p.has_gate ? 1 : 0);
+    const long wid = (long)blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (wid >= (long)p.n_tokens * items) return;
+    prep_item(p, (int)(wid / items), (int)(wid % items), threadIdx.x & 31, 0.f, 0.f, turn[threadIdx.x >> 5]);
+}
+
+// A CTA per token for the norm over whole rows: the sums of squares of the biased q row and k row first, each thread's
+// share in a fixed order and the warps' shares added in warp order, then the token's items dealt to the warps.
+__global__ void __launch_bounds__(THREADS) talking_prep_rows_kernel(PrepParams p) {
+    __shared__ float turn[WARPS][32 * MAX_PER_LANE];
+    __shared__ float part[2][WARPS];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = p.proj + (size_t)t * p.proj_stride;
+    const int nq = p.H * p.dk, nk = p.G * p.dk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += THREADS) {
+        const float v = row[i] + (p.bias ? load_any(p.bias, p.bias_dt, i) : 0.f);
+        sq = fmaf(v, v, sq);
+    }
+    for (int i = threadIdx.x; i < nk; i += THREADS) {
+        const float v = row[nq + i] + (p.bias ? load_any(p.bias, p.bias_dt, nq + i) : 0.f);
+        sk = fmaf(v, v, sk);
+    }
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    if (lane == 0) { part[0][warp] = sq; part[1][warp] = sk; }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) { tq += part[0][w]; tk += part[1][w]; }
+    const float inv_q = 1.0f / sqrtf(tq / (float)nq + p.eps), inv_k = 1.0f / sqrtf(tk / (float)nk + p.eps);
+    const int items = p.H + (p.write_kv ? 2 * p.G : 0) + (p.has_gate ? 1 : 0);
+    for (int item = warp; item < items; item += WARPS) prep_item(p, t, item, lane, inv_q, inv_k, turn[warp]);
+}
+
 struct AttnParams {
     const float* q; long q_stride;            // [T, H * dk]
     const float* gate;                        // [T, H] or null
@@ -119,7 +184,7 @@ struct AttnParams {
     const int* q_start; const int* kv_len; const int* work;     // work: (sequence, first query of the tile) pairs
     const float* talk; const float* sink;     // [H, H], [H]; either may be null
     void* out; int out_dt; long out_stride;   // [T, H * dv]
-    int H, G, dk, dv, window, QT; float scale;
+    int H, G, dk, dv, window, chunk, QT; float scale;
     int* status;
 };
 
@@ -142,7 +207,8 @@ __global__ void __launch_bounds__(THREADS) talking_attention_kernel(AttnParams p
     const int nq = min(QT, q_len - q0);
     const int pos0 = p.kv_len[s] - q_len + q0;          // position of the tile's first query
     const int k_end = pos0 + nq;                        // keys [k_begin, k_end) are seen by some query of the tile
-    const int k_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    int k_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    if (p.chunk > 0) k_begin = max(k_begin, pos0 / p.chunk * p.chunk);       // the first query's block starts no later than the others'
     const T* cache = reinterpret_cast<const T*>(p.cache);
     const size_t head_stride = (size_t)p.page_size * p.hdp;
 
@@ -206,7 +272,8 @@ __global__ void __launch_bounds__(THREADS) talking_attention_kernel(AttnParams p
             const int kk = i % KEY_TILE, qi = (i / KEY_TILE) % nq, h = i / (KEY_TILE * nq);
             const int kpos = k0 + kk, qpos = pos0 + qi;
             float v = -INFINITY;
-            if (kpos <= qpos && kpos >= k_begin && (p.window <= 0 || kpos > qpos - p.window) && key_at[kk] >= 0) {
+            if (kpos <= qpos && kpos >= k_begin && (p.window <= 0 || kpos > qpos - p.window)
+                && (p.chunk <= 0 || kpos >= qpos / p.chunk * p.chunk) && key_at[kk] >= 0) {
                 if (p.talk) {
                     v = 0.f;
                     for (int g = 0; g < H; ++g) v = fmaf(Tm[h * H + g], Sraw[(g * QT + qi) * KEY_TILE + kk], v);
@@ -269,19 +336,20 @@ RS_EXPORT int rs_talking_attention_q_per_cta(int H, int dk, int dv) {
 }
 
 RS_EXPORT int rs_talking_attention_prep(const float* proj, long proj_stride, const void* bias, int bias_dt, const void* q_norm,
-                                        const void* k_norm, int norm_dt, float eps, const float* cos_sin, int n_rot, int table_rows,
-                                        float* q_out, long q_stride, float* gate_out, void* cache, int cache_dt, long page_stride,
+                                        const void* k_norm, int norm_dt, float eps, int row_norm, const float* cos_sin, int n_rot,
+                                        int table_rows, int half_pairs, float* q_out, long q_stride, float* gate_out, void* cache, int cache_dt, long page_stride,
                                         int num_pages, int page_size, int hdp, const int* block_table, int table_stride,
                                         const int* positions, int pos_stride, const int* seq_of_token, int H, int G, int dk, int dv,
                                         int n_tokens, int write_kv, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dk > 32 * MAX_PER_LANE || dv > 32 * MAX_PER_LANE || hdp > 32 * MAX_PER_LANE || (n_rot & 1) || n_rot > dk)
         return (int)cudaErrorInvalidValue;
-    PrepParams p{proj, proj_stride, bias, bias_dt, q_norm, k_norm, norm_dt, eps, cos_sin, n_rot, table_rows, q_out, q_stride, gate_out,
+    PrepParams p{proj, proj_stride, bias, bias_dt, q_norm, k_norm, norm_dt, eps, row_norm, cos_sin, n_rot, table_rows, half_pairs, q_out, q_stride, gate_out,
                  cache, cache_dt, page_stride, (long)G * page_size * hdp, num_pages, page_size, hdp, block_table, table_stride,
                  positions, pos_stride, seq_of_token, H, G, dk, dv, n_tokens, write_kv, gate_out != nullptr, status};
     const long warps = (long)n_tokens * (H + (write_kv ? 2 * G : 0) + (gate_out ? 1 : 0));
-    talking_prep_kernel<<<(unsigned)((warps + WARPS - 1) / WARPS), THREADS, 0, stream>>>(p);
+    if (row_norm && q_norm) talking_prep_rows_kernel<<<(unsigned)n_tokens, THREADS, 0, stream>>>(p);
+    else talking_prep_kernel<<<(unsigned)((warps + WARPS - 1) / WARPS), THREADS, 0, stream>>>(p);
     return rs_launch_result();
 }
 
@@ -289,12 +357,12 @@ RS_EXPORT int rs_talking_attention(const float* q, long q_stride, const float* g
                                    int num_pages, int page_size, int hdp, const int* block_table, int table_stride,
                                    const int* q_start, const int* kv_len, const int* work, int n_work, const float* talk,
                                    const float* sink, void* out, int out_dt, long out_stride, int H, int G, int dk, int dv,
-                                   int window, int QT, float scale, int* status, cudaStream_t stream) {
+                                   int window, int chunk, int QT, float scale, int* status, cudaStream_t stream) {
     if (n_work <= 0) return 0;
     const size_t smem = attn_smem_bytes(H, QT, dk, dv);
     if (QT < 1 || smem > SMEM_LIMIT || H % G) return (int)cudaErrorInvalidValue;
     AttnParams p{q, q_stride, gate, cache, page_stride, (long)G * page_size * hdp, num_pages, page_size, hdp, block_table, table_stride,
-                 q_start, kv_len, work, talk, sink, out, out_dt, out_stride, H, G, dk, dv, window, QT, scale, status};
+                 q_start, kv_len, work, talk, sink, out, out_dt, out_stride, H, G, dk, dv, window, chunk, QT, scale, status};
     static bool sized = false;          // once: the attribute is a property of the function, not of a launch
     if (!sized) {
         cudaFuncSetAttribute(talking_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);

@@ -36,7 +36,7 @@ struct MmaParams {
     const float* talk; const float* sink;     // [H, H], [H]; either may be null
     void* out; int out_dt; long out_stride;   // [T, H * dv]
     float* partial; long partial_rows;        // [rows, H, dv + 2]: sums, maximum, denominator
-    int H, G, dk, dv, window, QT; float scale;
+    int H, G, dk, dv, window, chunk, QT; float scale;
     int* status;
 };
 
@@ -129,7 +129,8 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
     const int nq = min(QT, q_len - q0);
     const int pos0 = p.kv_len[s] - q_len + q0;
     const int k_end = pos0 + nq;
-    const int k_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    int k_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    if (p.chunk > 0) k_begin = max(k_begin, pos0 / p.chunk * p.chunk);      // chunked: nothing before the first query's block
     const int kt0 = k_begin / KEY_TILE, kt1 = (k_end + KEY_TILE - 1) / KEY_TILE;
     const int per = (kt1 - kt0 + parts - 1) / parts;
     const int t_begin = kt0 + part * per, t_end = min(kt1, t_begin + per);
@@ -245,7 +246,8 @@ __global__ void __launch_bounds__(THREADS, 1) talking_mma_kernel(MmaParams p) {
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const int kpos = k0 + kq * 4 + b;
-                seen[b] = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window) && at_now[kq * 4 + b] >= 0;
+                seen[b] = kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window)
+                          && (p.chunk <= 0 || kpos >= qpos / p.chunk * p.chunk) && at_now[kq * 4 + b] >= 0;
             }
 #pragma unroll
             for (int a = 0; a < 8; ++a) {
@@ -459,8 +461,8 @@ RS_EXPORT int rs_talking_attention_mma(const float* q, long q_stride, const floa
                                        int num_pages, int page_size, int hdp, const int* block_table, int table_stride,
                                        const int* q_start, const int* kv_len, const int* work, int n_work, int any_parts,
                                        const float* talk, const float* sink, void* out, int out_dt, long out_stride,
-                                       float* partial, long partial_rows, int H, int G, int dk, int dv, int window, int QT,
-                                       float scale, int* status, cudaStream_t stream) {
+                                       float* partial, long partial_rows, int H, int G, int dk, int dv, int window, int chunk,
+                                       int QT, float scale, int* status, cudaStream_t stream) {
     if (n_work <= 0) return 0;
     if (!shape_ok(H, G, dk, dv) || (QT != 4 && QT != 8 && QT != 16) || hdp % 8 || (any_parts && !partial))
         return (int)cudaErrorInvalidValue;
@@ -468,7 +470,7 @@ RS_EXPORT int rs_talking_attention_mma(const float* q, long q_stride, const floa
     if (smem > SMEM_LIMIT) return (int)cudaErrorInvalidValue;
     MmaParams p{q, q_stride, gate, reinterpret_cast<const __nv_bfloat16*>(cache), page_stride, (long)G * page_size * hdp, num_pages,
                 page_size, hdp, block_table, table_stride, q_start, kv_len, work, talk, sink, out, out_dt, out_stride, partial,
-                partial_rows, H, G, dk, dv, window, QT, scale, status};
+                partial_rows, H, G, dk, dv, window, chunk, QT, scale, status};
     int rc;
     if (H > WARPS) rc = launch<2, 4>(p, n_work, smem, stream);
     else if (dv <= 64) rc = launch<1, 4>(p, n_work, smem, stream);

@@ -93,7 +93,8 @@ def core():
         lib.rs_qk_norm_rope_kv.argtypes = [c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                            c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                            c_int, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p]
-        lib.rs_silu_mul.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p]
+        lib.rs_silu_mul.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rs_head_sigmoid_gate.argtypes = [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p]
         lib.rs_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_long, c_void_p]
         lib.rs_linear_simt.argtypes = [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_long,
                                        c_int, c_int, c_int, c_int, c_void_p]
@@ -252,8 +253,14 @@ def qk_norm_rope_kv(qkv: torch.Tensor, n_tokens: int, n_q: int, n_kv: int, head_
         n_tokens, _ptr(status), _stream()), "qk_norm_rope_kv")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
-    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, I + c], I = out.shape[1]."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int, activation: str = "silu") -> None:
+    """out[r, c] = act(gate_up[r, c]) * gate_up[r, I + c], I = out.shape[1]; act is SiLU or ("gelu_tanh") the tanh
+    form of GELU."""
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"silu_mul: unknown activation '{activation}' (known: {', '.join(sorted(GATE_ACTIVATIONS))})")
     _cuda(gate_up, out)
     _rows_contiguous(gate_up, "gate_up")
     _rows_contiguous(out, "out")
@@ -261,7 +268,18 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
     if gate_up.shape[1] != 2 * I or gate_up.dtype != out.dtype or n_rows > min(gate_up.shape[0], out.shape[0]):
         raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} does not fit out {tuple(out.shape)}")
     _check(core().rs_silu_mul(_ptr(gate_up), gate_up.stride(0), _ptr(out), out.stride(0), dtype_code(out), n_rows, I,
-                              _stream()), "silu_mul")
+                              GATE_ACTIVATIONS[activation], _stream()), "silu_mul")
+
+
+def head_sigmoid_gate(a: torch.Tensor, gate: torch.Tensor, n_heads: int, dv: int, n_tokens: int) -> None:
+    """a[t, h * dv + d] *= sigmoid(gate[t, h]) in place; gate float32 [T, >= heads] (pre-activations)."""
+    _cuda(a, gate)
+    _rows_contiguous(a, "head_sigmoid_gate a")
+    if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[1] < n_heads \
+            or a.shape[1] < n_heads * dv or n_tokens > min(a.shape[0], gate.shape[0]):
+        raise KernelError("head_sigmoid_gate: a [T, heads * dv], gate float32 [T, heads]")
+    _check(core().rs_head_sigmoid_gate(_ptr(a), dtype_code(a), a.stride(0), _ptr(gate), gate.stride(0), n_heads, dv, n_tokens,
+                                       _stream()), "head_sigmoid_gate")
 
 
 def residual_add(x: torch.Tensor, delta: torch.Tensor, n_rows: int) -> None:
@@ -1346,14 +1364,14 @@ def streamlib():
         lib = load_library("stream")
         lib.rs_embed_sum.argtypes = [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_long, c_long, c_void_p, c_int, c_int,
                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long,
-                                     c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                                     c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
         lib.rs_stream_layernorm.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                             c_float, c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p]
         lib.rs_stream_update.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                          c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_long, c_int, c_int, c_int,
                                          c_void_p]
-        lib.rs_router_topk.argtypes = [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                       c_void_p]
+        lib.rs_router_topk.argtypes = [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_void_p]
         lib.rs_conv_norm_kv_write.argtypes = [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p, c_long,
                                               c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -1377,8 +1395,9 @@ def _i32(name: str, *ts) -> None:
 def embed_sum(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, n_tokens: int, n_seqs: int, copies: int,
               positions: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
               status: torch.Tensor, bigram: Optional[torch.Tensor] = None, mul_prev: int = 0, mul_cur: int = 0,
-              prev_state: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None) -> None:
-    """out[t, c * D : (c + 1) * D] = table[ids[t]] + bigram[row(t)] + position_table[place(t)] for every copy c < copies
+              prev_state: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None,
+              scale: float = 1.0) -> None:
+    """out[t, c * D : (c + 1) * D] = scale * table[ids[t]] + bigram[row(t)] + position_table[place(t)] for every copy c < copies
     (float32).  ``bigram`` [buckets + 1, D]: row (previous token * mul_prev + token * mul_cur) mod buckets, the last
     row for a sequence's first token; the previous token of a portion's first token is read from ``prev_state``
     (int32 [slots, >= 1]), which then takes each sequence's last token.  ``positions`` [T, streams]: column 0 is the
@@ -1399,7 +1418,7 @@ def embed_sum(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, n_token
         int(mul_prev), int(mul_cur), _ptr(position_table), _any_code(position_table),
         0 if position_table is None else position_table.shape[0], _ptr(ids), _ptr(positions), positions.stride(0),
         _ptr(seq_of_token), _ptr(q_start), _ptr(slots), _ptr(prev_state), 0 if prev_state is None else prev_state.stride(0),
-        _ptr(out), out.stride(0), copies, D, n_tokens, n_seqs, _ptr(status), _stream()), "embed_sum",
+        _ptr(out), out.stride(0), copies, D, n_tokens, n_seqs, float(scale), _ptr(status), _stream()), "embed_sum",
         2 if bigram is not None else 1)
 
 
@@ -1455,9 +1474,13 @@ def stream_update(x: torch.Tensor, n_streams: int, y: torch.Tensor, mix: torch.T
 
 
 def router_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_tokens: int, choice: torch.Tensor,
-                weights: torch.Tensor, status: torch.Tensor) -> None:
-    """scores = softmax(logits[t]) (float32 [T, E]); choice[t] = the ``top`` experts with the largest score + correction
-    (int32 [T, top], the lower index on a tie); weights[t] = their scores / (sum of their scores + 1e-20)."""
+                weights: torch.Tensor, status: torch.Tensor, sigmoid: bool = False, groups: int = 0, keep: int = 0,
+                scale: float = 1.0, renormalize: bool = True) -> None:
+    """scores = softmax(logits[t]) (float32 [T, E]; ``sigmoid``: the sigmoid of every logit); choice[t] = the ``top``
+    experts with the largest score + correction (int32 [T, top], the lower index on a tie); with ``groups`` > 0 only
+    experts of the ``keep`` best of that many equal groups of neighbours (a group is worth its two largest scores +
+    correction added); weights[t] = their scores times ``scale``, over (the sum of their scores + 1e-20) first if
+    ``renormalize``."""
     _cuda(logits, correction, choice, weights, status)
     _rows_contiguous(logits, "router_topk logits")
     E = logits.shape[1]
@@ -1466,8 +1489,12 @@ def router_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: i
         raise KernelError("router_topk: logits float32 [T, E], choice int32 and weights float32 [T * top] contiguous")
     if not 1 <= top <= E <= 1024 or (correction is not None and correction.numel() != E):
         raise KernelError(f"router_topk: top {top} of {E} experts (up to 1024), one correction per expert")
+    if groups and (E % groups or not 1 <= keep <= groups or top > keep * (E // groups)):
+        raise KernelError(f"router_topk: {groups} groups of {E} experts, {keep} kept, top {top}")
     _check(streamlib().rs_router_topk(_ptr(logits), logits.stride(0), _ptr(correction), _any_code(correction), E, top,
-                                      n_tokens, _ptr(choice), _ptr(weights), _ptr(status), _stream()), "router_topk")
+                                      n_tokens, 1 if sigmoid else 0, int(groups), int(keep), float(scale),
+                                      1 if renormalize else 0, _ptr(choice), _ptr(weights), _ptr(status), _stream()),
+           "router_topk")
 
 
 def conv_norm_kv_write(proj: torch.Tensor, conv_weight: Optional[torch.Tensor], tails: Optional[torch.Tensor], n_q: int,
@@ -1543,21 +1570,23 @@ def mixerslib():
                                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]
         lib.rs_head_norm_gate.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_int,
-                                          c_float, c_int, c_void_p]
+                                          c_float, c_int, c_int, c_void_p]
+        lib.rs_retention_prep.argtypes = [c_void_p, c_long, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         lib.rs_activation.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.rs_scale_rows.argtypes = [c_void_p, c_long, c_int, c_int, c_float, c_void_p]
         lib.rs_talking_attention_q_per_cta.argtypes = [c_int, c_int, c_int]
-        lib.rs_talking_attention_prep.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int,
-                                                  c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int,
+        lib.rs_talking_attention_prep.argtypes = [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p,
+                                                  c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int,
                                                   c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                   c_void_p, c_void_p]
         lib.rs_talking_attention.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_long, c_int,
-                                             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+                                             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
         lib.rs_talking_attention_mma_q_per_cta.argtypes = [c_int, c_int, c_int, c_int]
         lib.rs_talking_attention_mma.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_int,
                                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                 c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                 c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                                  c_void_p, c_void_p]
         _mixerslib = lib
     return _mixerslib
@@ -1653,9 +1682,30 @@ def delta_prep(proj: torch.Tensor, conv: Optional[torch.Tensor], tail: Optional[
         float(unit_eps), float(q_scale), n_tokens, n_seqs, _stream()), "delta_prep", 2 if taps > 1 else 1)
 
 
+def retention_prep(proj: torch.Tensor, cos_sin: Optional[torch.Tensor], n_rot: int, positions: torch.Tensor, k_scale: float,
+                   q: torch.Tensor, k: torch.Tensor, heads: int, dim: int, rows_pad: int, n_tokens: int,
+                   status: torch.Tensor) -> None:
+    """From proj [T, q | k | ...] (float32): every q and k head with its first ``n_rot`` coordinates turned by the token's
+    position (coordinate i with i + n_rot / 2, ``cos_sin`` [positions, cos | sin]), k times ``k_scale`` afterwards; q and k
+    [T, heads * rows_pad] contiguous, padding zero."""
+    _cuda(proj, cos_sin, positions, q, k, status)
+    _f32_rows("retention_prep", proj=proj, q=q, k=k, cos_sin=cos_sin)
+    _i32("retention_prep", positions)
+    if proj.shape[1] < 2 * heads * dim or any(t.shape[1] != heads * rows_pad or not t.is_contiguous() for t in (q, k)) \
+            or rows_pad < dim:
+        raise KernelError("retention_prep: shapes do not fit heads x dim")
+    if n_rot and (cos_sin is None or cos_sin.shape[1] != n_rot or not cos_sin.is_contiguous() or n_rot > dim or n_rot % 2):
+        raise KernelError("retention_prep: the rotation table must be contiguous [positions, n_rot] with n_rot even and <= dim")
+    _check(mixerslib().rs_retention_prep(_ptr(proj), proj.stride(0), _ptr(cos_sin), n_rot if cos_sin is not None else 0,
+                                         0 if cos_sin is None else cos_sin.shape[0], _ptr(positions), positions.stride(0),
+                                         float(k_scale), _ptr(q), _ptr(k), heads, dim, rows_pad, n_tokens, _ptr(status),
+                                         _stream()), "retention_prep")
+
+
 def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor, heads: int,
-                   vdim: int, eps: float, n_tokens: int) -> None:
-    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * sigmoid(gate[t, h, :]); o and gate float32."""
+                   vdim: int, eps: float, n_tokens: int, gate_silu: bool = False) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * sigmoid(gate[t, h, :]) (``gate_silu``: times
+    silu(gate) instead); o and gate float32."""
     _cuda(o, weight, gate, out)
     _f32_rows("head_norm_gate", o=o, gate=gate)
     _rows_contiguous(out, "head_norm_gate out")
@@ -1664,7 +1714,7 @@ def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Option
         raise KernelError("head_norm_gate: shapes do not fit heads x vdim")
     _check(mixerslib().rs_head_norm_gate(_ptr(o), o.stride(0), _ptr(weight), _any_code(weight), _ptr(gate),
                                          0 if gate is None else gate.stride(0), _ptr(out), dtype_code(out), out.stride(0), heads,
-                                         vdim, float(eps), n_tokens, _stream()), "head_norm_gate")
+                                         vdim, float(eps), n_tokens, 1 if gate_silu else 0, _stream()), "head_norm_gate")
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, n_rows: int, kind: str, params: Optional[torch.Tensor] = None) -> None:
@@ -1701,9 +1751,12 @@ def talking_attention_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_n
                            k_norm: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], n_rot: int,
                            q_out: torch.Tensor, gate_out: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
                            page_size: int, positions: torch.Tensor, seq_of_token: torch.Tensor, n_heads: int, n_kv: int, dk: int,
-                           dv: int, n_tokens: int, write_kv: bool, status: torch.Tensor) -> None:
-    """proj [T, q | k | v | gate] float32 (+ bias): RMS norm of q and k heads (weights [dk], None: none), rotation of
-    the first ``n_rot`` coordinates in neighbouring pairs by ``cos_sin`` [positions, cos | sin], q to ``q_out`` float32
+                           dv: int, n_tokens: int, write_kv: bool, status: torch.Tensor, row_norm: bool = False,
+                           half_pairs: bool = False) -> None:
+    """proj [T, q | k | v | gate] float32 (+ bias): RMS norm of q and k heads (weights [dk], None: none; ``row_norm``: one
+    norm over the whole q row and one over the whole k row, weights [heads * dk] and [n_kv * dk]), rotation of
+    the first ``n_rot`` coordinates by ``cos_sin`` [positions, cos | sin] in neighbouring pairs (``half_pairs``: coordinate
+    i with i + n_rot / 2), q to ``q_out`` float32
     [T, heads * dk], k and v into ``cache`` [pages, 2, n_kv, page_size, head_pad] (padding zero), sigmoid of the gates
     to ``gate_out`` float32 [T, heads]."""
     _cuda(proj, bias, q_norm, k_norm, cos_sin, q_out, gate_out, cache, block_table, positions, seq_of_token, status)
@@ -1716,14 +1769,16 @@ def talking_attention_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_n
             or tuple(cache.shape[1:]) != (2, n_kv, page_size, hdp) or hdp < max(dk, dv) \
             or (gate_out is not None and (gate_out.shape[1] != n_heads or not gate_out.is_contiguous())):
         raise KernelError("talking_attention_prep: shapes do not fit the head counts and sizes")
-    if (q_norm is None) != (k_norm is None) or (q_norm is not None and (q_norm.numel() != dk or k_norm.numel() != dk
+    nq_w, nk_w = (n_heads * dk, n_kv * dk) if row_norm else (dk, dk)
+    if (q_norm is None) != (k_norm is None) or (q_norm is not None and (q_norm.numel() != nq_w or k_norm.numel() != nk_w
                                                                         or q_norm.dtype != k_norm.dtype)):
-        raise KernelError("talking_attention_prep: q and k norm weights come together, [dk] each, one element type")
+        raise KernelError(f"talking_attention_prep: q and k norm weights come together, [{nq_w}] and [{nk_w}], one element type")
     if n_rot and (cos_sin is None or cos_sin.shape[1] != n_rot or not cos_sin.is_contiguous()):
         raise KernelError("talking_attention_prep: the rotation table must be contiguous [positions, n_rot]")
     _check(mixerslib().rs_talking_attention_prep(
         _ptr(proj), proj.stride(0), _ptr(bias), _any_code(bias), _ptr(q_norm), _ptr(k_norm), _any_code(q_norm), float(eps),
-        _ptr(cos_sin), n_rot if cos_sin is not None else 0, 0 if cos_sin is None else cos_sin.shape[0], _ptr(q_out),
+        1 if row_norm else 0, _ptr(cos_sin), n_rot if cos_sin is not None else 0, 0 if cos_sin is None else cos_sin.shape[0],
+        1 if half_pairs else 0, _ptr(q_out),
         q_out.stride(0), _ptr(gate_out), _ptr(cache), dtype_code(cache), cache.stride(0), cache.shape[0], page_size, hdp,
         _ptr(block_table), block_table.stride(0), _ptr(positions), positions.stride(0), _ptr(seq_of_token), n_heads, n_kv, dk, dv,
         n_tokens, 1 if write_kv else 0, _ptr(status), _stream()), "talking_attention_prep")
@@ -1732,8 +1787,9 @@ def talking_attention_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_n
 def talking_attention(q: torch.Tensor, gate: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
                       page_size: int, q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int,
                       talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], out: torch.Tensor, n_heads: int, n_kv: int,
-                      dk: int, dv: int, window: int, q_per_cta: int, scale: float, status: torch.Tensor) -> None:
-    """Causal attention of the step's queries over the paged cache with scores mixed across heads (``talk`` float32
+                      dk: int, dv: int, window: int, q_per_cta: int, scale: float, status: torch.Tensor, chunk: int = 0) -> None:
+    """Causal attention of the step's queries over the paged cache (within ``window`` keys if positive, within the query's
+    own block of ``chunk`` positions if positive) with scores mixed across heads (``talk`` float32
     [heads, heads]: mixed[h] = sum_g talk[h, g] raw[g]) before a softmax whose denominator also holds exp(sink[h]);
     every head's output times ``gate`` [T, heads].  ``work``: (sequence, first query) per tile of ``q_per_cta`` queries."""
     _cuda(q, gate, cache, block_table, q_start, kv_len, work, talk, sink, out, status)
@@ -1749,8 +1805,8 @@ def talking_attention(q: torch.Tensor, gate: Optional[torch.Tensor], cache: torc
     _check(mixerslib().rs_talking_attention(
         _ptr(q), q.stride(0), _ptr(gate), _ptr(cache), dtype_code(cache), cache.stride(0), cache.shape[0], page_size,
         cache.shape[-1], _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, _ptr(talk),
-        _ptr(sink), _ptr(out), dtype_code(out), out.stride(0), n_heads, n_kv, dk, dv, window, q_per_cta, float(scale),
-        _ptr(status), _stream()), "talking_attention")
+        _ptr(sink), _ptr(out), dtype_code(out), out.stride(0), n_heads, n_kv, dk, dv, window, int(chunk), q_per_cta,
+        float(scale), _ptr(status), _stream()), "talking_attention")
 
 
 def talking_attention_mma_q_per_cta(n_heads: int, n_kv: int, dk: int, dv: int) -> int:
@@ -1766,7 +1822,7 @@ def talking_attention_mma(q: torch.Tensor, gate: Optional[torch.Tensor], cache: 
                           page_size: int, q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int,
                           any_parts: bool, talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], out: torch.Tensor,
                           partial: Optional[torch.Tensor], n_heads: int, n_kv: int, dk: int, dv: int, window: int, q_per_cta: int,
-                          scale: float, status: torch.Tensor) -> None:
+                          scale: float, status: torch.Tensor, chunk: int = 0) -> None:
     """``talking_attention`` for a bfloat16 cache on the tensor cores (csrc/talking_attention_mma.cu).  ``work`` rows are
     (sequence, first query, part, parts, first partial row): a tile's key tiles are dealt out over ``parts`` CTAs, whose
     sums meet in ``partial`` float32 [rows, >= heads * (dv + 2)] (part p of a tile of n queries uses rows first + p * n ..)."""
@@ -1792,4 +1848,4 @@ def talking_attention_mma(q: torch.Tensor, gate: Optional[torch.Tensor], cache: 
         _ptr(q), q.stride(0), _ptr(gate), _ptr(cache), cache.stride(0), cache.shape[0], page_size, cache.shape[-1],
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, 1 if any_parts else 0,
         _ptr(talk), _ptr(sink), _ptr(out), dtype_code(out), out.stride(0), _ptr(partial), rows, n_heads, n_kv, dk, dv, window,
-        q_per_cta, float(scale), _ptr(status), _stream()), "talking_attention_mma")
+        int(chunk), q_per_cta, float(scale), _ptr(status), _stream()), "talking_attention_mma")

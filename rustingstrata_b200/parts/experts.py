@@ -171,17 +171,22 @@ class TableMoE(FeedForward):
 
 @register_part("feed_forward", "routed_moe")
 class RoutedMoE(FeedForward):
-    """A mixture of experts chosen per token by a softmax router, with an optional shared expert.
+    """A mixture of experts chosen per token by a router, with an optional shared expert.
 
-    Router logits z = W_r h and scores s = softmax(z) over all experts are float32 in both engines.  The ``top``
-    experts with the largest s + correction are chosen (``correction``: one learned number per expert that steers the
-    choice only); their weights are their scores s divided by the sum of the chosen scores (+ 1e-20).  An expert is
-    down(relu(up h)^2) without biases; a shared expert of the same form runs for every token and is added unweighted.
+    Router logits z = W_r h are float32 in both engines; the scores s are softmax(z) over all experts (``score``
+    "softmax") or sigmoid(z), each expert for itself ("sigmoid").  The ``top`` experts with the largest s + correction are
+    chosen (``correction``: one learned number per expert that steers the choice only).  With ``groups`` the experts form
+    that many equal groups of neighbours; a group is worth the sum of its two largest s + correction, and only experts
+    of the ``keep`` groups worth most can be chosen.  The weights are the chosen experts' scores s times ``route_scale``,
+    divided by the sum of the chosen scores (+ 1e-20) first if ``renormalize``.  An expert (``expert``) is "relu2":
+    down(relu(up h)^2), or "gated_silu": down(silu(gate h) * (up h)), without biases; a shared expert of the same form
+    runs for every token and is added unweighted.
 
-    params: hidden, experts, top, expert_ff, shared_ff (0 or None: no shared expert), correction (bool).
-    tensors: router [experts, hidden], correction [experts]; expert_up / expert_down: name patterns with ``{e}`` for the
-    expert's number; shared_up, shared_down.  The step's (token, k) pairs are sorted by expert on the device and one
-    grouped product per projection serves all experts, as in :class:`TableMoE`."""
+    params: hidden, experts, top, expert_ff, shared_ff (0 or None: no shared expert), correction (bool), score, groups
+    (0 or None: none), keep, route_scale (default 1), renormalize (default True), expert (default "relu2").
+    tensors: router [experts, hidden], correction [experts]; expert_up / expert_down (and expert_gate): name patterns
+    with ``{e}`` for the expert's number; shared_up, shared_down (and shared_gate).  The step's (token, k) pairs are sorted
+    by expert on the device and one grouped product per projection serves all experts, as in :class:`TableMoE`."""
     SMALL_PAIRS_PER_EXPERT = TableMoE.SMALL_PAIRS_PER_EXPERT
     LARGE_PAIRS_PER_EXPERT = TableMoE.LARGE_PAIRS_PER_EXPERT
 
@@ -193,8 +198,22 @@ class RoutedMoE(FeedForward):
         self.ff = int(p["expert_ff"])
         self.shared_ff = int(p.get("shared_ff") or 0)
         self.has_correction = bool(p.get("correction", False))
+        self.score = p.get("score", "softmax")
+        self.groups, self.keep = int(p.get("groups") or 0), int(p.get("keep") or 0)
+        self.route_scale = float(p.get("route_scale", 1.0))
+        self.renormalize = bool(p.get("renormalize", True))
+        self.form = p.get("expert", "relu2")
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"routed_moe: score {self.score!r} (known: 'softmax', 'sigmoid')")
+        if self.form not in ("relu2", "gated_silu"):
+            raise ValueError(f"routed_moe: expert form {self.form!r} (known: 'relu2', 'gated_silu')")
+        self.gated = self.form == "gated_silu"
         if not 1 <= self.top <= self.n_experts <= 1024:
             raise ValueError(f"routed_moe: top {self.top} of {self.n_experts} experts (up to 1024)")
+        if self.groups and (self.n_experts % self.groups or not 1 <= self.keep <= self.groups
+                            or self.top > self.keep * (self.n_experts // self.groups)):
+            raise ValueError(f"routed_moe: {self.groups} groups of {self.n_experts} experts with {self.keep} kept cannot "
+                             f"give {self.top} experts")
         rt = runtime
         pairs = rt.max_batch_tokens * self.top
         self.act_name = f"moe_act_{self.ff}"
@@ -209,6 +228,8 @@ class RoutedMoE(FeedForward):
         if self.shared_ff:
             rt.scratch("moe_shared_act", rt.max_batch_tokens, self.shared_ff)
             rt.scratch("moe_shared_out", rt.max_batch_tokens, self.hidden, torch.float32)
+            if self.gated:
+                rt.scratch("moe_shared_gu", rt.max_batch_tokens, 2 * self.shared_ff)
 
     def _max_tiles(self, pairs: int, rows: int) -> int:
         return pairs // rows + min(self.n_experts, pairs)
@@ -219,9 +240,13 @@ class RoutedMoE(FeedForward):
         if self.has_correction:
             needs[t["correction"]] = TensorNeed((self.n_experts,))
         for e in range(self.n_experts):
+            if self.gated:
+                needs[t["expert_gate"].format(e=e)] = TensorNeed((self.ff, self.hidden))
             needs[t["expert_up"].format(e=e)] = TensorNeed((self.ff, self.hidden))
             needs[t["expert_down"].format(e=e)] = TensorNeed((self.hidden, self.ff))
         if self.shared_ff:
+            if self.gated:
+                needs[t["shared_gate"]] = TensorNeed((self.shared_ff, self.hidden))
             needs[t["shared_up"]] = TensorNeed((self.shared_ff, self.hidden))
             needs[t["shared_down"]] = TensorNeed((self.hidden, self.shared_ff))
         return needs
@@ -230,17 +255,34 @@ class RoutedMoE(FeedForward):
         t, E = self.spec.tensors, self.n_experts
         self.w_router = tensors[t["router"]].contiguous()
         self.correction = tensors[t["correction"]].to(torch.float32).contiguous() if self.has_correction else None
-        self.w_up = torch.stack([tensors[t["expert_up"].format(e=e)] for e in range(E)]).contiguous()
-        self.w_down = torch.stack([tensors[t["expert_down"].format(e=e)] for e in range(E)]).contiguous()
+        u0 = tensors[t["expert_up"].format(e=0)]
         # bfloat16 engine with 16-byte aligned rows: the grouped products run on the tensor cores
-        self.tensor_cores = (self.w_up.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16
+        self.tensor_cores = (u0.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16
                              and self.hidden % 8 == 0 and self.ff % 8 == 0)
+        if self.gated:
+            # on the tensor cores gate and up rows alternate, so that the grouped product finds a gate and its up in
+            # neighbouring accumulator columns; else gate rows first, up rows behind them
+            join = (lambda g, u: torch.stack([g, u], dim=1).reshape(2 * self.ff, self.hidden)) if self.tensor_cores else \
+                (lambda g, u: torch.cat([g, u], dim=0))
+            self.w_up = torch.stack([join(tensors[t["expert_gate"].format(e=e)], tensors[t["expert_up"].format(e=e)])
+                                     for e in range(E)]).contiguous()
+        else:
+            self.w_up = torch.stack([tensors[t["expert_up"].format(e=e)] for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[t["expert_down"].format(e=e)] for e in range(E)]).contiguous()
         if self.shared_ff:
             self.w_shared_up = tensors[t["shared_up"]].contiguous()
             self.w_shared_down = tensors[t["shared_down"]].contiguous()
+            if self.gated:
+                g, u = tensors[t["shared_gate"]], self.w_shared_up
+                self.shared_fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0)
+                if self.shared_fused:      # gate and up rows alternate: the product's epilogue applies SiLU(gate) * up
+                    self.w_shared_up = torch.stack([g, u], dim=1).reshape(2 * self.shared_ff, self.hidden).contiguous()
+                else:
+                    self.w_shared_up = torch.cat([g, u], dim=0).contiguous()
 
     def flops_per_token(self) -> float:
-        return 2.0 * (2 * self.top * self.ff * self.hidden + 2 * self.shared_ff * self.hidden + self.n_experts * self.hidden)
+        m = 3 if self.gated else 2
+        return 2.0 * (m * self.top * self.ff * self.hidden + m * self.shared_ff * self.hidden + self.n_experts * self.hidden)
 
     def forward(self, h, residual, ctx: StepContext):
         rt, T, top = self.runtime, ctx.n_tokens, self.top
@@ -259,20 +301,30 @@ class RoutedMoE(FeedForward):
         choice = rt.get_scratch("router_choice", torch.int32).view(-1)[:pairs]
         weights = rt.get_scratch("router_weights", torch.float32).view(-1)[:pairs]
         ops.linear(h, self.w_router, logits, T, status=ctx.status)
-        ops.router_topk(logits, self.correction, top, T, choice, weights, ctx.status)
+        ops.router_topk(logits, self.correction, top, T, choice, weights, ctx.status, sigmoid=self.score == "sigmoid",
+                        groups=self.groups, keep=self.keep, scale=self.route_scale, renormalize=self.renormalize)
         ops.moe_route(None, choice.view(T, top), self.n_experts, T, rows, order, tiles, n_tiles, ctx.status)
         if tensor_cores:
-            ops.grouped_gemm_mma(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, large=large, relu2=True)
+            ops.grouped_gemm_mma(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=self.gated, large=large,
+                                 relu2=not self.gated)
             ops.grouped_gemm_mma(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, large=large)
         else:
-            ops.grouped_linear(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=False, small=small, relu2=True)
+            ops.grouped_linear(h, top, self.w_up, act, order, tiles, n_tiles, max_tiles, gated=self.gated, small=small,
+                               relu2=not self.gated)
             ops.grouped_linear(act, 1, self.w_down, pair_out, order, tiles, n_tiles, max_tiles, gated=False, small=small)
         shared_out = None
         if self.shared_ff:
             sact = rt.get_scratch("moe_shared_act")[:, : self.shared_ff]
             shared_out = rt.get_scratch("moe_shared_out", torch.float32)[:, : self.hidden]
-            ops.linear(h, self.w_shared_up, sact, T, status=ctx.status)
-            ops.relu_squared(sact, sact, T)
+            if not self.gated:
+                ops.linear(h, self.w_shared_up, sact, T, status=ctx.status)
+                ops.relu_squared(sact, sact, T)
+            elif self.shared_fused:
+                ops.linear_swiglu(h, self.w_shared_up, sact, T, status=ctx.status)
+            else:
+                gu = rt.get_scratch("moe_shared_gu")[:, : 2 * self.shared_ff]
+                ops.linear(h, self.w_shared_up, gu, T)
+                ops.silu_mul(gu, sact, T)
             ops.linear(sact, self.w_shared_down, shared_out, T, status=ctx.status)
         if ctx.store_output:
             ops.moe_combine(pair_out, top, 1.0, residual, T, shared=shared_out, pair_weights=weights)

@@ -17,7 +17,7 @@ from .spec import TensorNeed
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
-    """params: hidden, intermediate, activation ("silu").  tensors: gate_proj, up_proj, down_proj."""
+    """params: hidden, intermediate, activation ("silu", the default, or "gelu_tanh").  tensors: gate_proj, up_proj, down_proj."""
     chain_safe = True
 
     def __init__(self, spec, runtime):
@@ -25,8 +25,9 @@ class GatedMLP(FeedForward):
         self.hidden = int(spec.params["hidden"])
         self.inter = int(spec.params["intermediate"])
         act = spec.params.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"gated_mlp: activation '{act}' has no kernel (only 'silu')")
+        if act not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation '{act}' has no kernel (known: {', '.join(sorted(ops.GATE_ACTIVATIONS))})")
+        self.activation = act
         runtime.scratch("gate_up", runtime.max_batch_tokens, 2 * self.inter)
         runtime.scratch("ff_act", runtime.max_batch_tokens, self.inter)
         self.w_gate_up = self.w_down = None
@@ -45,7 +46,8 @@ class GatedMLP(FeedForward):
         # bfloat16 engine with 16-byte aligned rows: gate and up rows alternate, so the product's epilogue
         # applies SiLU(gate)*up to neighbouring accumulator columns and the [T, 2I] intermediate never
         # reaches memory.  Otherwise [gate; up] stacked, followed by the separate activation kernel.
-        self.fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0)
+        self.fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                      and self.activation == "silu")
         if self.fused:
             self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden).contiguous()
         else:
@@ -61,7 +63,7 @@ class GatedMLP(FeedForward):
             ops.linear_swiglu(h, self.w_gate_up, act, T, status=ctx.status)
         else:
             ops.linear(h, self.w_gate_up, gate_up, T)
-            ops.silu_mul(gate_up, act, T)
+            ops.silu_mul(gate_up, act, T, self.activation)
         ctx.owed = ops.linear(act, self.w_down, residual, T, accumulate=not ctx.store_output, status=ctx.status,
                               may_defer=ctx.may_owe and not ctx.store_output)
 

@@ -5,6 +5,9 @@ W_dkv h = [latent part (kv_rank) | one rotated key part (rot_dim) shared by all 
 the latent; head k's key is [W_uk,k c | rotated part], its value W_uv,k c, and a score is
 (q_unrotated . k_unrotated + q_rotated . k_rotated) * scale over the causal keys, softmax, W_o on the joined heads.
 
+``rot_dim`` may be 0 (no rotated parts, no position part).  With ``gate`` every head's result is multiplied by
+sigmoid(w_g[h] . h), one number per token and head, before W_o.
+
 Only [c | rotated key part] is cached: one row per token (a one-plane cache, one "kv head" that every query head
 reads).  The expansion is folded into the query and the result, which gives the same numbers:
 
@@ -29,8 +32,8 @@ from .spec import CacheNeed, PartSpec, TensorNeed
 @register_part("mixer", "latent_attention")
 class LatentAttention(PagedAttention):
     """params: hidden, n_heads, dim (unrotated query/key size per head), rot_dim, vdim, kv_rank, scale, eps (of the
-    latent's norm).  tensors: q_proj, dkv_proj, latent_norm, uk_proj [heads * dim, kv_rank], uv_proj [heads * vdim,
-    kv_rank], o_proj.  The layer's position part rotates the first ``n_rot`` <= rot_dim coordinates of the rotated
+    latent's norm), window (None: every key), gate (bool, default False).  tensors: q_proj, dkv_proj, latent_norm, uk_proj
+    [heads * dim, kv_rank], uv_proj [heads * vdim, kv_rank], o_proj, and g_proj [heads, hidden] with a gate.  The layer's position part rotates the first ``n_rot`` <= rot_dim coordinates of the rotated
     parts (pairs (2i, 2i + 1): a part whose ``pairing`` is "interleaved")."""
     chain_safe = False
     one_plane = True
@@ -51,6 +54,8 @@ class LatentAttention(PagedAttention):
         self.spec = spec
         self._tensor_cores = None
         self.latent_eps = float(p["eps"])
+        self.has_gate = bool(p.get("gate", False))
+        self.dkv_cols = self.rank + self.rot_dim + (self.n_heads if self.has_gate else 0)
         if position is not None and getattr(position, "cos_sin", None) is not None:
             if getattr(position, "pairing", "") != "interleaved":
                 raise ValueError("latent_attention rotates neighbouring pairs: its position part must be an interleaved rotation")
@@ -58,22 +63,30 @@ class LatentAttention(PagedAttention):
                 raise ValueError(f"latent_attention: {position.n_rot} rotated coordinates exceed rot_dim {self.rot_dim}")
         rt = runtime
         rt.scratch("latent_q", rt.max_batch_tokens, self.n_heads * self.q_head)
-        rt.scratch("latent_dkv", rt.max_batch_tokens, self.rank + self.rot_dim, torch.float32)
+        rt.scratch("latent_dkv", rt.max_batch_tokens, self.dkv_cols, torch.float32)
         rt.scratch("latent_o", rt.max_batch_tokens, self.n_heads * self.vdim)
 
     def tensor_needs(self):
         t, H = self.spec.tensors, self.n_heads
-        return {t["q_proj"]: TensorNeed((H * self.q_head, self.hidden)),
-                t["dkv_proj"]: TensorNeed((self.rank + self.rot_dim, self.hidden)),
-                t["latent_norm"]: TensorNeed((self.rank,), "norm"),
-                t["uk_proj"]: TensorNeed((H * self.dim, self.rank)),
-                t["uv_proj"]: TensorNeed((H * self.vdim, self.rank)),
-                t["o_proj"]: TensorNeed((self.hidden, H * self.vdim))}
+        needs = {t["q_proj"]: TensorNeed((H * self.q_head, self.hidden)),
+                 t["dkv_proj"]: TensorNeed((self.rank + self.rot_dim, self.hidden)),
+                 t["latent_norm"]: TensorNeed((self.rank,), "norm"),
+                 t["uk_proj"]: TensorNeed((H * self.dim, self.rank)),
+                 t["uv_proj"]: TensorNeed((H * self.vdim, self.rank)),
+                 t["o_proj"]: TensorNeed((self.hidden, H * self.vdim))}
+        if self.has_gate:
+            needs[t["g_proj"]] = TensorNeed((H, self.hidden))
+        return needs
 
     def load(self, tensors):
         t, H = self.spec.tensors, self.n_heads
         self.w_q = tensors[t["q_proj"]].contiguous()
         self.w_dkv = tensors[t["dkv_proj"]].contiguous()
+        if self.has_gate:
+            g = tensors[t["g_proj"]]
+            if g.dtype != self.w_dkv.dtype:
+                raise ValueError("latent_attention: the gate's and the latent's projections must share an element type")
+            self.w_dkv = torch.cat([self.w_dkv, g], dim=0).contiguous()      # [latent | rotated key part | gates]: one product
         self.latent_norm = tensors[t["latent_norm"]].contiguous()
         # head k's key expansion transposed: [rank, dim], the map from its unrotated query to the latent's coordinates
         self.w_uk_t = tensors[t["uk_proj"]].reshape(H, self.dim, self.rank).transpose(1, 2).contiguous()
@@ -116,7 +129,7 @@ class LatentAttention(PagedAttention):
     def flops_per_token(self) -> float:
         """Multiply-add flops of the products one token passes (the folded form the kernels run)."""
         H = self.n_heads
-        return 2.0 * (H * self.q_head * self.hidden + (self.rank + self.rot_dim) * self.hidden + H * self.rank * self.dim
+        return 2.0 * (H * self.q_head * self.hidden + self.dkv_cols * self.hidden + H * self.rank * self.dim
                       + H * self.vdim * self.rank + self.hidden * H * self.vdim)
 
     def forward(self, h, residual, ctx: StepContext, call: CallInfo):
@@ -124,7 +137,7 @@ class LatentAttention(PagedAttention):
         if not call.writes_cache:
             raise RuntimeError("latent_attention: every call owns its cache")
         q = rt.get_scratch("latent_q")[:, : H * self.q_head]
-        dkv = rt.get_scratch("latent_dkv", torch.float32)[:, : self.rank + self.rot_dim]
+        dkv = rt.get_scratch("latent_dkv", torch.float32)[:, : self.dkv_cols]
         q_lat = rt.get_scratch("qkv")[:, : H * self.lat]
         o = rt.get_scratch("latent_o")[:, : H * self.vdim]
         ops.linear(h, self.w_q, q, T, status=ctx.status)
@@ -138,4 +151,6 @@ class LatentAttention(PagedAttention):
                             H, T, ctx.status)
         out = self._attend(q_lat, ctx, call)
         ops.block_linear(out, self.w_uv, o, T, self.lat, self.vdim)
+        if self.has_gate:
+            ops.head_sigmoid_gate(o, dkv[:, self.rank + self.rot_dim:], H, self.vdim, T)
         ops.linear(o, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)

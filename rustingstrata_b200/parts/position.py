@@ -16,8 +16,11 @@ from .registry import register_part
 
 @register_part("position", "rope_neox")
 class RotaryNeox(PositionEncoding):
-    """params: n_rot (rotated dims of a head), base."""
+    """params: n_rot (rotated dims of a head), base, base_bits (32, the default: the base is held as float32 and widened,
+    as the reference holds it; 64: the base as config.json gives it).  Coordinate i < n_rot / 2 turns together with
+    i + n_rot / 2 (``pairing`` "half")."""
     chain_safe = True
+    pairing = "half"
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -25,7 +28,12 @@ class RotaryNeox(PositionEncoding):
         self.base = float(spec.params["base"])
         if self.n_rot % 2:
             raise ValueError(f"rope_neox: n_rot {self.n_rot} must be even")
-        self._key = ("rope_neox", self.n_rot, self.base, runtime.max_positions)
+        self.base_bits = int(spec.params.get("base_bits", 32))
+        if self.base_bits not in (32, 64):
+            raise ValueError(f"rope_neox: base_bits {self.base_bits} (32 or 64)")
+        # as many positions as a request can reach: the model's limit, or what the cache pool holds if that is less
+        self.rows = max(1, min(runtime.max_positions, runtime.pool_tokens))
+        self._key = ("rope_neox", self.n_rot, self.base, self.base_bits, self.rows)
 
     @property
     def cos_sin(self) -> torch.Tensor:
@@ -36,8 +44,9 @@ class RotaryNeox(PositionEncoding):
         half = self.n_rot // 2
         i = np.arange(half, dtype=np.float64)
         # the reference holds the base as float32 and widens it (src/ops.rs:39)
-        inv = np.power(np.float64(np.float32(self.base)), -2.0 * i / self.n_rot)
-        theta = np.arange(self.runtime.max_positions, dtype=np.float64)[:, None] * inv[None, :]
+        base = np.float64(np.float32(self.base)) if self.base_bits == 32 else np.float64(self.base)
+        inv = np.power(base, -2.0 * i / self.n_rot)
+        theta = np.arange(self.rows, dtype=np.float64)[:, None] * inv[None, :]
         tab = np.concatenate([np.cos(theta), np.sin(theta)], axis=1).astype(np.float32)
         return torch.from_numpy(tab).to(self.runtime.device)
 

@@ -1,5 +1,6 @@
-"""Mixers that keep a matrix of state per head in place of a cache of keys: HGRN2 and the gated delta rule with a decay
-per key channel.  Both walk a float32 state S [dim, vdim] per (request, head) token by token and read it out with a query.
+"""Mixers that keep a matrix of state per head in place of a cache of keys: HGRN2, the gated delta rule with a decay
+per key channel, and retention with one fixed decay per head.  All walk a float32 state S [dim, vdim] per (request, head)
+token by token and read it out with a query.
 
 ``hgrn2`` (gated linear recurrence whose forget gate also decides what is written).  From the mixer's input h:
 q = silu(W_q h), v = W_v h, f = l + (1 - l) sigmoid(W_f h + b_f) per head and channel, l a learned lower bound;
@@ -18,6 +19,15 @@ beta = sigmoid(W_b h) per head; g = exp(-exp(A_h) softplus(W_a2 (W_a1 h) + dt)) 
 
 (the read-out sees the token's own write); each head's o_t divided by its root mean square over vdim, times a weight
 [vdim] shared by the heads, times sigmoid(W_g2 (W_g1 h)) laid out heads x vdim; then W_o.
+
+``retention`` (linear attention with a fixed decay per head, no softmax and no denominator).  q = W_q h, k = W_k h
+(heads x dim), v = W_v h (heads x vdim), no biases; the layer's position part rotates a prefix of every q and k head;
+k times dim^-1/2 after the rotation;
+
+    S_t = decay_h S_(t-1) + k_t v_t^T,        o_t = S_t^T q_t;
+
+each head's o_t is divided by its root mean square over vdim (no weight), the heads are joined, multiplied by
+silu(W_g h) coordinate by coordinate, and W_o maps them back.
 
 Per request the state slot holds S for every head (zero at admission) and, for the convolution, the last taps - 1
 projected rows.  The projections follow the engine's element type with float32 results; gates, decays, norms, the
@@ -198,4 +208,83 @@ class GatedDelta(Mixer):
         ops.state_recurrence(q, k, g, beta, v, read, state, ctx.q_start, ctx.state_slots, ctx.n_seqs, H, H // G, RP, self.dv,
                              delta=True)
         ops.head_norm_gate(read, self.norm_w, gate, out, H, self.dv, self.eps, T)
+        ops.linear(out, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)
+
+
+@register_part("mixer", "retention")
+class Retention(Mixer):
+    """params: hidden, n_heads, dim, vdim, decay (one number per head), eps (of the read-out norm), k_scale (default
+    dim^-1/2), gate (bool, default True: the normed heads times silu(g_proj h)).
+    tensors: q_proj, k_proj, v_proj, o_proj, and g_proj [heads * vdim, hidden] with a gate.  The layer's position part,
+    if it has a rotation, must pair halves (coordinate i with i + n_rot / 2)."""
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden, self.n_heads = int(p["hidden"]), int(p["n_heads"])
+        self.dk, self.dv = int(p["dim"]), int(p["vdim"])
+        self.decay = [float(d) for d in p["decay"]]
+        if len(self.decay) != self.n_heads:
+            raise ValueError(f"retention: {len(self.decay)} decays for {self.n_heads} heads")
+        self.eps = float(p.get("eps", 0.0))
+        self.k_scale = float(p["k_scale"]) if p.get("k_scale") is not None else float(self.dk) ** -0.5
+        self.has_gate = bool(p.get("gate", True))
+        self.position = position
+        self.n_rot = int(getattr(position, "n_rot", 0) or 0)
+        if self.n_rot and getattr(position, "pairing", "half") != "half":
+            raise ValueError("retention: its kernel pairs the halves of the rotated prefix; the position part pairs otherwise")
+        if self.n_rot > self.dk:
+            raise ValueError(f"retention: {self.n_rot} rotated coordinates in heads of {self.dk}")
+        self.rows_pad = ops.state_rows_pad(self.dk)
+        self.qk_cols, self.v_cols = self.n_heads * self.dk, self.n_heads * self.dv
+        self.in_cols = 2 * self.qk_cols + self.v_cols * (2 if self.has_gate else 1)
+        rt = runtime
+        rt.scratch("state_proj", rt.max_batch_tokens, self.in_cols, torch.float32)
+        rt.scratch("state_rows", 1, 2 * rt.max_batch_tokens * self.n_heads * self.rows_pad, torch.float32)
+        rt.scratch("state_read", rt.max_batch_tokens, self.v_cols, torch.float32)
+        rt.scratch("state_out", rt.max_batch_tokens, self.v_cols)
+        self.decay_rows = None
+
+    def tensor_needs(self):
+        t = self.spec.tensors
+        needs = {t["q_proj"]: TensorNeed((self.qk_cols, self.hidden)), t["k_proj"]: TensorNeed((self.qk_cols, self.hidden)),
+                 t["v_proj"]: TensorNeed((self.v_cols, self.hidden)), t["o_proj"]: TensorNeed((self.hidden, self.v_cols))}
+        if self.has_gate:
+            needs[t["g_proj"]] = TensorNeed((self.v_cols, self.hidden))
+        return needs
+
+    def load(self, tensors):
+        t = self.spec.tensors
+        mats = [tensors[t[n]] for n in ("q_proj", "k_proj", "v_proj")] + ([tensors[t["g_proj"]]] if self.has_gate else [])
+        if len({m.dtype for m in mats}) != 1:
+            raise ValueError("retention: the input projections must share an element type")
+        self.w_in = torch.cat(mats, dim=0).contiguous()              # [q | k | v | gate]: h is read by one product
+        self.w_o = tensors[t["o_proj"]].contiguous()
+        # the decay of every row of every head, one row that all tokens read
+        d = torch.tensor(self.decay, dtype=torch.float32).view(self.n_heads, 1).expand(self.n_heads, self.rows_pad)
+        self.decay_rows = d.reshape(1, -1).contiguous().to(self.w_o.device)
+
+    def state_need(self):
+        return StateNeed(self.n_heads * self.dv * self.rows_pad, "float32")
+
+    def flops_per_token(self) -> float:
+        return 2.0 * self.hidden * (self.in_cols + self.v_cols) + 6.0 * self.n_heads * self.dk * self.dv
+
+    def forward(self, h, residual, ctx: StepContext, call: CallInfo):
+        rt, T, H, RP = self.runtime, ctx.n_tokens, self.n_heads, self.rows_pad
+        proj = rt.get_scratch("state_proj", torch.float32)[:, : self.in_cols]
+        n = rt.max_batch_tokens * H * RP
+        rows = rt.get_scratch("state_rows", torch.float32)[0]
+        q, k = (rows[i * n:(i + 1) * n].view(rt.max_batch_tokens, H * RP) for i in range(2))
+        read = rt.get_scratch("state_read", torch.float32)[:, : self.v_cols]
+        out = rt.get_scratch("state_out")[:, : self.v_cols]
+        ops.linear(h, self.w_in, proj, T, status=ctx.status)
+        rot = getattr(self.position, "cos_sin", None) if self.n_rot else None
+        ops.retention_prep(proj, rot, self.n_rot, ctx.positions, self.k_scale, q, k, H, self.dk, RP, T, ctx.status)
+        g = self.decay_rows.expand(T, H * RP)                        # pitch 0: the same decays for every token
+        v_off = 2 * self.qk_cols
+        ops.state_recurrence(q, k, g, None, proj[:, v_off: v_off + self.v_cols], read, call.state, ctx.q_start,
+                             ctx.state_slots, ctx.n_seqs, H, 1, RP, self.dv, delta=False)
+        gate = proj[:, v_off + self.v_cols:] if self.has_gate else None
+        ops.head_norm_gate(read, None, gate, out, H, self.dv, self.eps, T, gate_silu=True)
         ops.linear(out, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)

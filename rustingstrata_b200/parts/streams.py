@@ -24,7 +24,8 @@ from .spec import StateNeed, TensorNeed
 class TableSumEmbedding(Part):
     """Token row + bigram row + learned position row, written to every residual stream.
 
-    params: vocab, width, copies (residual streams to fill, default 1); bigram: None or {buckets, mul_prev, mul_cur}: row
+    params: vocab, width, copies (residual streams to fill, default 1), scale (default 1: multiplies the token row);
+    bigram: None or {buckets, mul_prev, mul_cur}: row
     (previous token * mul_prev + token * mul_cur) mod buckets of a [buckets + 1, width] table whose last row serves a
     sequence's first token; positions: rows of a learned [positions, width] table added unscaled, or 0 for none.
     tensors: weight, and bigram / position when the params have them.  Per request it keeps one int32: the last token
@@ -35,6 +36,7 @@ class TableSumEmbedding(Part):
         p = spec.params
         self.vocab, self.width = int(p["vocab"]), int(p["width"])
         self.copies = int(p.get("copies", 1))
+        self.scale = float(p.get("scale", 1.0))
         big = p.get("bigram")
         self.bigram_params = None if big is None else (int(big["buckets"]), int(big["mul_prev"]), int(big["mul_cur"]))
         if self.bigram_params is not None and self.bigram_params[0] < 1:
@@ -67,7 +69,7 @@ class TableSumEmbedding(Part):
         ops.embed_sum(self.weight, ctx.token_ids, residual, ctx.n_tokens, ctx.n_seqs, self.copies, ctx.positions,
                       ctx.seq_of_token, ctx.q_start, ctx.state_slots, ctx.status, bigram=self.bigram,
                       mul_prev=big[1] if big else 0, mul_cur=big[2] if big else 0, prev_state=self.state,
-                      position_table=self.position)
+                      position_table=self.position, scale=self.scale)
 
 
 @register_part("norm", "layernorm")

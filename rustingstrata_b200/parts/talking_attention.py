@@ -3,12 +3,15 @@ in every head's denominator and a sigmoid gate per head.
 
 Per token, from the mixer's input h:  q = W_q h + b_q (heads x dim), k = W_k h + b_k, v = W_v h + b_v (kv heads x dim /
 vdim; query head i reads kv head i // (heads / kv heads)).  Every q and k head is divided by its root mean square and
-multiplied by a weight of ``dim`` values shared by the heads; the position encoding then rotates the first ``n_rot``
-coordinates of each q and k head.  With raw[g, i, j] = (q_gi . k_gj) * scale the score of head h is
+multiplied by a weight of ``dim`` values shared by the heads (``norm`` "head"), or the whole q row and the whole k row
+are each divided by their root mean square and multiplied by a weight per coordinate (``norm`` "row"); the position
+encoding then rotates the first ``n_rot`` coordinates of each q and k head, in neighbouring pairs or, for a part that
+pairs halves, coordinate i with i + n_rot / 2.  With raw[g, i, j] = (q_gi . k_gj) * scale the score of head h is
 
     mixed[h, i, j] = sum_g talk[h, g] raw[g, i, j]                      (talk [heads, heads]; None: the raw score)
 
-and the weights of query i over the keys j <= i (within ``window`` if there is one) are
+and the weights of query i over the keys j <= i (within ``window`` if there is one; with ``chunk`` only keys of the
+query's own block of that many positions, floor(i / chunk) = floor(j / chunk), blocks counted from position 0) are
 
     exp(mixed[h, i, j]) / (exp(sink[h]) + sum_j' exp(mixed[h, i, j']))  (sink [heads]; None: no such term).
 
@@ -38,9 +41,10 @@ PARTIAL_ROWS = 4096        # (query, part) rows of partial sums the workspace ho
 
 @register_part("mixer", "talking_attention")
 class TalkingAttention(Mixer):
-    """params: hidden, n_heads, n_kv_heads, dim, vdim, scale, eps, window (None: every key), bias, qk_norm, talk, sink,
-    gate (bools, default True).  tensors: q_proj, k_proj, v_proj, o_proj, and as the params ask q_bias, k_bias, v_bias,
-    q_norm, k_norm, talk [heads, heads], sink [heads], g_proj [heads, hidden]."""
+    """params: hidden, n_heads, n_kv_heads, dim, vdim, scale, eps, window (None: every key), chunk (None: no blocks),
+    bias, qk_norm, talk, sink, gate (bools, default True), norm ("head", the default, or "row").  tensors: q_proj, k_proj,
+    v_proj, o_proj, and as the params ask q_bias, k_bias, v_bias, q_norm, k_norm ([dim] each; "row": [heads * dim] and
+    [kv heads * dim]), talk [heads, heads], sink [heads], g_proj [heads, hidden]."""
 
     def __init__(self, spec, runtime, position=None):
         super().__init__(spec, runtime)
@@ -51,6 +55,10 @@ class TalkingAttention(Mixer):
         self.scale = float(p["scale"])
         self.eps = float(p.get("eps", 0.0))
         self.window = int(p["window"]) if p.get("window") else 0
+        self.chunk = int(p["chunk"]) if p.get("chunk") else 0
+        self.row_norm = p.get("norm", "head") == "row"
+        if p.get("norm", "head") not in ("head", "row"):
+            raise ValueError(f"talking_attention: norm {p.get('norm')!r} (known: 'head', 'row')")
         self.has_bias, self.qk_norm = bool(p.get("bias", True)), bool(p.get("qk_norm", True))
         self.has_talk, self.has_sink, self.has_gate = bool(p.get("talk", True)), bool(p.get("sink", True)), bool(p.get("gate", True))
         self.position = position
@@ -59,8 +67,7 @@ class TalkingAttention(Mixer):
         if max(self.dk, self.dv) > 256:
             raise ValueError(f"talking_attention: head sizes {self.dk} / {self.dv} exceed the 256 the kernels take")
         n_rot = int(getattr(position, "n_rot", 0) or 0)
-        if n_rot and getattr(position, "pairing", "") != "interleaved":
-            raise ValueError("talking_attention: its kernels rotate neighbouring pairs; the position encoding pairs otherwise")
+        self.half_pairs = bool(n_rot) and getattr(position, "pairing", "half") != "interleaved"
         if n_rot > self.dk:
             raise ValueError(f"talking_attention: {n_rot} rotated coordinates in heads of {self.dk}")
         self.head_pad = (max(self.dk, self.dv) + 7) // 8 * 8           # cache rows start on 16 bytes in both element types
@@ -87,7 +94,8 @@ class TalkingAttention(Mixer):
             needs.update({t["q_bias"]: TensorNeed((self.q_cols,)), t["k_bias"]: TensorNeed((self.k_cols,)),
                           t["v_bias"]: TensorNeed((self.v_cols,))})
         if self.qk_norm:
-            needs.update({t["q_norm"]: TensorNeed((self.dk,), "norm"), t["k_norm"]: TensorNeed((self.dk,), "norm")})
+            nq, nk = (self.q_cols, self.k_cols) if self.row_norm else (self.dk, self.dk)
+            needs.update({t["q_norm"]: TensorNeed((nq,), "norm"), t["k_norm"]: TensorNeed((nk,), "norm")})
         if self.has_talk:
             needs[t["talk"]] = TensorNeed((self.n_heads, self.n_heads), "average")
         if self.has_sink:
@@ -112,7 +120,9 @@ class TalkingAttention(Mixer):
 
     # ---------------------------------------------------------------- what it keeps
     def cache_need(self):
-        return CacheNeed(self.n_kv, self.head_pad, self.window or None)
+        # a block of ``chunk`` positions never reaches further back than chunk keys, the query's own included
+        reach = [w for w in (self.window, self.chunk) if w]
+        return CacheNeed(self.n_kv, self.head_pad, min(reach) if reach else None)
 
     def flops_per_token(self) -> float:
         return 2.0 * self.hidden * (self.in_cols + self.o_in)
@@ -121,7 +131,10 @@ class TalkingAttention(Mixer):
         pairs = 0.0
         for q, kv in zip(np.asarray(q_lens, dtype=np.int64), np.asarray(kv_lens, dtype=np.int64)):
             pos = np.arange(kv - q, kv, dtype=np.float64)
-            pairs += float((pos + 1 if not self.window else np.minimum(pos + 1, self.window)).sum())
+            seen = pos + 1 if not self.window else np.minimum(pos + 1, self.window)
+            if self.chunk:
+                seen = np.minimum(seen, pos % self.chunk + 1)
+            pairs += float(seen.sum())
         mix = 2.0 * self.n_heads * self.n_heads if self.has_talk else 0.0
         return (2.0 * self.n_heads * (self.dk + self.dv) + mix) * pairs
 
@@ -134,7 +147,7 @@ class TalkingAttention(Mixer):
 
     def plan_key(self):
         self._setup()
-        return ("talking_attention", self.q_per_cta, self.mma_q, self.window)
+        return ("talking_attention", self.q_per_cta, self.mma_q, self.window, self.chunk)
 
     def build_plan(self, batch: HostBatch):
         """Tiles of neighbouring queries of one sequence, the ones with the most keys to walk first.  For the tensor-core
@@ -165,6 +178,8 @@ class TalkingAttention(Mixer):
                 parts[:] = share              # a captured step: the launch shape must not follow the lengths
             else:
                 begin = np.maximum(0, first - self.window + 1) if self.window else np.zeros(n, dtype=np.int64)
+                if self.chunk:
+                    begin = np.maximum(begin, first // self.chunk * self.chunk)
                 key_tiles = -(-(first + nq) // KEY_TILE) - begin // KEY_TILE
                 parts = np.clip(key_tiles // MIN_PART_TILES, 1, share)
             while int((parts * nq)[parts > 1].sum()) > PARTIAL_ROWS:
@@ -192,16 +207,17 @@ class TalkingAttention(Mixer):
         rot = getattr(pos, "cos_sin", None) if pos is not None else None
         ops.talking_attention_prep(proj, self.bias, self.q_norm_w, self.k_norm_w, self.eps, rot,
                                    int(pos.n_rot) if rot is not None else 0, q, gate, call.cache, table, rt.page_size,
-                                   ctx.positions, ctx.seq_of_token, self.n_heads, self.n_kv, self.dk, self.dv, T, True, ctx.status)
+                                   ctx.positions, ctx.seq_of_token, self.n_heads, self.n_kv, self.dk, self.dv, T, True, ctx.status,
+                                   row_norm=self.row_norm, half_pairs=self.half_pairs)
         plan = ctx.plans[self.plan_key()]
         if self.mma_q:
             partial = rt.get_scratch("talk_partial", torch.float32) if plan["any_parts"] else None
             ops.talking_attention_mma(q, gate, call.cache, table, rt.page_size, ctx.q_start, ctx.kv_len, plan["work"],
                                       plan["n_work"], bool(plan["any_parts"]), self.talk, self.sink, out, partial, self.n_heads,
-                                      self.n_kv, self.dk, self.dv, self.window, plan["qt"], self.scale, ctx.status)
+                                      self.n_kv, self.dk, self.dv, self.window, plan["qt"], self.scale, ctx.status, chunk=self.chunk)
         else:
             # a step of single tokens: a CTA's shared memory is sized for its one query
             ops.talking_attention(q, gate, call.cache, table, rt.page_size, ctx.q_start, ctx.kv_len, plan["work"],
                                   plan["n_work"], self.talk, self.sink, out, self.n_heads, self.n_kv, self.dk, self.dv,
-                                  self.window, plan["qt"], self.scale, ctx.status)
+                                  self.window, plan["qt"], self.scale, ctx.status, chunk=self.chunk)
         ops.linear(out, self.w_o, residual, T, accumulate=not ctx.store_output, status=ctx.status)
