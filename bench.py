@@ -95,8 +95,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run this many of the configuration's layers (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
-    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex", "tabedra", "kupelix"])
-    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex, tabedra or kupelix: widths to run")
+    ap.add_argument("--workload", default="headline", choices=["headline", "14b-mixed", "32b-long", "lokinex", "tabedra", "kupelix", "kozasun"])
+    ap.add_argument("--sizes", default="1024,2048", help="with --workload lokinex, tabedra, kupelix or kozasun: widths to run")
     ap.add_argument("--marginal", action="store_true", help="marginal cost of each kernel family inside the decode step")
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="with --marginal: tokens each request holds")
     ap.add_argument("--marginal-prefill", action="store_true",
@@ -121,7 +121,7 @@ def main() -> int:
         return long_context_workload(args)
     if args.workload == "lokinex":
         return lokinex_workload(args)
-    if args.workload in ("tabedra", "kupelix"):
+    if args.workload in ("tabedra", "kupelix", "kozasun"):
         return lokinex_workload(args, design=args.workload)
 
     import numpy as np
@@ -418,6 +418,32 @@ def kupelix_config(width: int) -> dict:
             "loop": {"start": 0, "stop": 4, "times": 2}}
 
 
+KOZASUN_MASK = 1024
+
+
+def kozasun_config(width: int) -> dict:
+    """A Kozasun model whose layers resemble real ones at this width: heads of 128 query/key and 128 value coordinates in
+    all three mixers; attention with one key/value head per four query heads, half of each head rotated and blocks of
+    1,024 positions; retention with decays 1 - 2^-(5 + h); latent attention over a latent of width / 4 with a window of
+    1,024 keys; a dense feed-forward of 4 x width or 32 experts of 3/4 width in 4 groups of which 2 are kept, 4 per token,
+    and a shared expert of 3/2 width; two residual streams; eight layer runs (attention + dense, retention + experts,
+    latent attention + dense, latent attention + experts, twice, the second attention layer with the first one's tensors)."""
+    heads = width // 128
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                          "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 64}, "mask": {"size": KOZASUN_MASK}}}
+    ret = {"type": "retention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 128},
+                                          "decay": [1.0 - 2.0 ** -(5 + h % 8) for h in range(heads)]}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": width // 4,
+                                                 "scale": 128 ** -0.5, "mask": {"size": KOZASUN_MASK}}}
+    moe = {"kind": "moe", "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": width * 3 // 4}, "shared": {"ff": width * 3 // 2}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Kozasun", "vocab": 32768, "width": width, "norm": {"eps": 1e-5}, "streams": 2,
+            "embedding": {"scale": 1.0}, "max_positions": 8192,
+            "layers": [dict(att, mlp=dense), dict(ret, mlp=moe), dict(lat, mlp=dense), dict(lat, mlp=moe),
+                       dict(att, mlp=dense, weights_of=0), dict(ret, mlp=moe), dict(lat, mlp=dense), dict(lat, mlp=moe)]}
+
+
 def qwen3_windowed(width: int) -> dict:
     """The closest existing model for the Tabedra design: the Qwen3 decoder of :func:`qwen3_like` with the same sliding
     window on every layer and as many key/value heads."""
@@ -442,7 +468,8 @@ class OpTimer:
              "grouped_gemm_mma", "attention_latent", "linear", "linear_swiglu", "qk_norm_rope_kv", "attention_prefill", "attention_decode",
              "attention_decode_items", "silu_mul", "residual_add", "sample", "latent_expand", "embed_sum", "stream_layernorm",
              "stream_update", "router_topk", "conv_norm_kv_write", "sigmoid_gate", "talking_attention_prep", "talking_attention", "talking_attention_mma",
-             "state_recurrence", "hgrn2_prep", "delta_prep", "head_norm_gate", "activation", "scale_rows")
+             "state_recurrence", "hgrn2_prep", "delta_prep", "head_norm_gate", "activation", "scale_rows", "retention_prep",
+             "head_sigmoid_gate")
 
     def __init__(self):
         self.events, self.real = [], {}
@@ -496,12 +523,13 @@ def lokinex_workload(args, design: str = "lokinex") -> int:
     clocks = ClockSampler()
     clocks.start()
     pair = {"lokinex": (lokinex_config, qwen3_like), "tabedra": (tabedra_config, qwen3_windowed),
-            "kupelix": (kupelix_config, qwen3_like)}[design]
+            "kupelix": (kupelix_config, qwen3_like), "kozasun": (kozasun_config, kupelix_config)}[design]
     out = {"workload": design, "prompt_len": PROMPT, "batch": args.batch, "steps": args.steps, "dtype": "bf16",
            "data": "synthetic", "weights": "random N(0,0.02) bf16", "peaks": pk["source"], "sizes": {}}
     for width in [int(x) for x in args.sizes.split(",")]:
         rec = {}
-        for name, cfg in ((design, pair[0](width)), ("qwen3", pair[1](width))):
+        other = "kupelix" if design == "kozasun" else "qwen3"        # the closest existing model of the design
+        for name, cfg in ((design, pair[0](width)), (other, pair[1](width))):
             V = cfg.get("vocab", cfg.get("vocab_size"))
             eng = Engine(cfg, dtype="bfloat16", random_seed=0, page_size=16, max_tokens=args.batch * CONTEXT,
                          max_batch_tokens=PROMPT, max_seqs=args.batch)
