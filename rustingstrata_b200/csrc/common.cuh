@@ -43,6 +43,18 @@ __device__ __forceinline__ float load_any(const void* p, int dt, size_t i) {
 // exp(-gate) overflows, a slow path of over a hundred cycles, which showed in the products of many rows.  Every
 // bfloat16 kernel uses this one function, so they agree to the bit; the 32-bit path divides exactly.
 __device__ __forceinline__ float silu_mul_fast(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+// The tanh form of GELU, 0.5 z (1 + tanh(y)) with y = sqrt(2 / pi) (z + 0.044715 z^3), times up, for the same epilogues:
+// 0.5 (1 + tanh(y)) = 1 / (1 + exp(-2 y)), so it costs what SiLU costs.
+__device__ __forceinline__ float gelu_tanh_mul_fast(float gate, float up) {
+    const float y = 0.7978845608028654f * fmaf(0.044715f * gate * gate, gate, gate);
+    return __fdividef(gate, 1.0f + __expf(-2.0f * y)) * up;
+}
+// Epilogue codes of the bfloat16 products that gate: 3 SiLU(gate) * up, 4 GELU(gate) * up (tanh form).
+#define RS_EPI_GATED(e) ((e) == 3 || (e) == 4)
+template <int EPI>
+__device__ __forceinline__ float gated_mul_fast(float gate, float up) {
+    return EPI == 4 ? gelu_tanh_mul_fast(gate, up) : silu_mul_fast(gate, up);
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -27,7 +27,7 @@ constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;      // 16 KiB
 constexpr int THREADS = 192;
 
-enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_GEGLU_BF16 = 4 };
 
 template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
@@ -118,7 +118,7 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int nmax) {
     // r: 32 consecutive accumulator columns [col0, col0 + 32) of output row `row`; columns from nmax on are not this tile's
     if (row >= p.M) return;
-    if (EPI == EPI_SWIGLU_BF16) {
+    if (RS_EPI_GATED(EPI)) {
         // columns alternate gate, up: out[row, (col0 + 2j) / 2] = silu(gate_j) * up_j
         const int half_n = nmax >> 1, oc0 = col0 >> 1;
         __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + oc0;
@@ -128,7 +128,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
             for (int j = 0; j < 8; ++j) {
                 const float g0 = __uint_as_float(r[4 * j]), u0 = __uint_as_float(r[4 * j + 1]);
                 const float g1 = __uint_as_float(r[4 * j + 2]), u1 = __uint_as_float(r[4 * j + 3]);
-                __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul_fast(g0, u0), silu_mul_fast(g1, u1));
+                __nv_bfloat162 v = __floats2bfloat162_rn(gated_mul_fast<EPI>(g0, u0), gated_mul_fast<EPI>(g1, u1));
                 packed[j] = *reinterpret_cast<uint32_t*>(&v);
             }
             reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -138,7 +138,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
             for (int j = 0; j < 16; ++j) {
                 if (oc0 + j < half_n) {
                     const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-                    out[j] = __float2bfloat16_rn(silu_mul_fast(g, u));
+                    out[j] = __float2bfloat16_rn(gated_mul_fast<EPI>(g, u));
                 }
             }
         }
@@ -293,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // bfloat16 results go the same way, two chunks (bf16 store) or four (SiLU(gate) * up: 16 results per chunk) to
         // a row of 128 bytes.
         const bool tma_out = p.out_by_tma;
-        constexpr int CHUNKS_PER_ROW = (EPI == EPI_STORE_BF16) ? 2 : (EPI == EPI_SWIGLU_BF16 ? 4 : 1);
+        constexpr int CHUNKS_PER_ROW = (EPI == EPI_STORE_BF16) ? 2 : (RS_EPI_GATED(EPI) ? 4 : 1);
         uint8_t* my_stage = out_stage + (warp - 2) * 2 * 4096;
         uint32_t n_out = 0;
         pdl_wait();
@@ -341,7 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 4; ++j) {
                                 const float g0 = __uint_as_float(r[16 * q + 4 * j]), u0 = __uint_as_float(r[16 * q + 4 * j + 1]);
                                 const float g1 = __uint_as_float(r[16 * q + 4 * j + 2]), u1 = __uint_as_float(r[16 * q + 4 * j + 3]);
-                                __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul_fast(g0, u0), silu_mul_fast(g1, u1));
+                                __nv_bfloat162 v = __floats2bfloat162_rn(gated_mul_fast<EPI>(g0, u0), gated_mul_fast<EPI>(g1, u1));
                                 w[j] = *reinterpret_cast<uint32_t*>(&v);
                             }
                             *reinterpret_cast<uint4*>(dst + lane * 128 + (((part * 2 + q) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -353,8 +353,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (lane == 0) {
                         // first result column of the row: accumulator column / 2 for SiLU(gate) * up
                         const int c_first = n0 + c - 32 * (CHUNKS_PER_ROW - 1);
-                        const int x = EPI == EPI_SWIGLU_BF16 ? c_first >> 1 : c_first;
-                        if (x < (EPI == EPI_SWIGLU_BF16 ? p.N >> 1 : p.N)) {          // else the whole row lies past the last column
+                        const int x = RS_EPI_GATED(EPI) ? c_first >> 1 : c_first;
+                        if (x < (RS_EPI_GATED(EPI) ? p.N >> 1 : p.N)) {          // else the whole row lies past the last column
                             if (EPI == EPI_ADD_F32) tma_add_2d(&map_c, smem_u32(dst), x, m0 + quarter * 32);
                             else tma_store_2d(&map_c, smem_u32(dst), x, m0 + quarter * 32);
                         }
@@ -436,6 +436,7 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const CUte
         case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(ma, mw, mc, p, max_ctas, s);
         case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(ma, mw, mc, p, max_ctas, s);
         case EPI_SWIGLU_BF16: return launch<BN, EPI_SWIGLU_BF16>(ma, mw, mc, p, max_ctas, s);
+        case EPI_GEGLU_BF16: return launch<BN, EPI_GEGLU_BF16>(ma, mw, mc, p, max_ctas, s);
     }
     return (int)cudaErrorInvalidValue;
 }
@@ -446,7 +447,7 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const CUte
 RS_EXPORT int rs_gemm_tc_supported(long a_ptr, long lda, long w_ptr, long ldw, int N, int K, int epi) {
     if (K <= 0 || N <= 0 || K % 8 || lda % 8 || ldw % 8) return 0;
     if ((a_ptr & 15) || (w_ptr & 15)) return 0;
-    if (epi == EPI_SWIGLU_BF16 && (N & 1)) return 0;
+    if (RS_EPI_GATED(epi) && (N & 1)) return 0;
     return 1;
 }
 
@@ -485,13 +486,13 @@ RS_EXPORT int rs_gemm_bf16_tc(const void* A, long lda, long a_rows, const void* 
     if (rc) return rc;
     GemmParams p;
     p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status; p.bn = bn;
-    const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
+    const int out_elem = (epi == EPI_STORE_BF16 || RS_EPI_GATED(epi)) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
     // results go out through the TMA unit when a tile's columns fill whole 128-byte rows of the staging tiles
     CUtensorMap mc = ma;
-    const int acc_cols_per_row = out_elem == 4 ? 32 : (epi == EPI_SWIGLU_BF16 ? 128 : 64);
+    const int acc_cols_per_row = out_elem == 4 ? 32 : (RS_EPI_GATED(epi) ? 128 : 64);
     p.out_by_tma = p.vec_ok && bn % acc_cols_per_row == 0 &&
-                   c_map(C, ldc, M, epi == EPI_SWIGLU_BF16 ? N / 2 : N, out_elem, &mc) == 0;
+                   c_map(C, ldc, M, RS_EPI_GATED(epi) ? N / 2 : N, out_elem, &mc) == 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (tpl == 256) return launch_epi<256>(epi, ma, mw, mc, p, max_ctas, s);
     if (tpl == 128 && bn == 128) return launch_epi<128>(epi, ma, mw, mc, p, max_ctas, s);

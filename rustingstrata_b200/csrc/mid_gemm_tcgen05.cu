@@ -41,7 +41,7 @@ constexpr int W_BYTES = W_BOX_BYTES * BOXES;
 constexpr int THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
-enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_GEGLU_BF16 = 4 };
 
 struct MidParams {
     void* C; long ldc;
@@ -93,11 +93,11 @@ using rs_streamk::cta_of_unit;
 // one finished value of C: row m of A, row n of W (all 32 lanes of a warp call this together, n consecutive)
 template <int EPI>
 __device__ __forceinline__ void store_value(const MidParams& p, float v, int m, int n) {
-    if (EPI == EPI_SWIGLU_BF16) {
+    if (RS_EPI_GATED(EPI)) {
         // rows of W alternate gate, up: the even lane of a pair writes
         const float up = __shfl_xor_sync(0xffffffffu, v, 1);
         if ((n & 1) == 0 && n + 1 < p.N)
-            ((__nv_bfloat16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul_fast(v, up));
+            ((__nv_bfloat16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gated_mul_fast<EPI>(v, up));
     } else if (n < p.N) {
         const size_t o = (size_t)m * p.ldc + n;
         if (EPI == EPI_STORE_BF16) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(v);
@@ -110,9 +110,9 @@ __device__ __forceinline__ void store_value(const MidParams& p, float v, int m, 
 // (read by the caller ahead of time) when the epilogue accumulates
 template <int EPI>
 __device__ __forceinline__ void store_four(const MidParams& p, float4 v, float4 old, int m, int n0) {
-    if (EPI == EPI_SWIGLU_BF16) {
+    if (RS_EPI_GATED(EPI)) {
         __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)m * p.ldc + (n0 >> 1);
-        const float a = silu_mul_fast(v.x, v.y), b = silu_mul_fast(v.z, v.w);
+        const float a = gated_mul_fast<EPI>(v.x, v.y), b = gated_mul_fast<EPI>(v.z, v.w);
         if (p.vec_ok && n0 + 3 < p.N) {
             *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(a, b);
         } else {
@@ -413,6 +413,7 @@ int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const MidP
         case EPI_STORE_F32: return launch<MP, EPI_STORE_F32>(mw, ma, p, max_ctas, defer, s);
         case EPI_ADD_F32: return launch<MP, EPI_ADD_F32>(mw, ma, p, max_ctas, defer, s);
         case EPI_SWIGLU_BF16: return launch<MP, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, defer, s);
+        case EPI_GEGLU_BF16: return launch<MP, EPI_GEGLU_BF16>(mw, ma, p, max_ctas, defer, s);
     }
     return (int)cudaErrorInvalidValue;
 }
@@ -434,7 +435,7 @@ RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void*
     if (M > 128 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
         workspace == nullptr)
         return (int)cudaErrorInvalidValue;
-    if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
+    if (RS_EPI_GATED(epi) && (N & 1)) return (int)cudaErrorInvalidValue;
     if (defer && epi != EPI_ADD_F32) return (int)cudaErrorInvalidValue;
     const int mp = padded_rows(M);
     CUtensorMap mw, ma;
@@ -445,7 +446,7 @@ RS_EXPORT int rs_mid_gemm_bf16(const void* A, long lda, long a_rows, const void*
     MidParams p;
     p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.stages = 0; p.workspace = workspace;
     p.status = status;
-    const int out_elem = (epi == EPI_STORE_BF16 || epi == EPI_SWIGLU_BF16) ? 2 : 4;
+    const int out_elem = (epi == EPI_STORE_BF16 || RS_EPI_GATED(epi)) ? 2 : 4;
     p.vec_ok = (((long)C & 15) == 0 && (ldc * out_elem) % 16 == 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (mp == 16) return launch_epi<16>(epi, mw, ma, p, max_ctas, defer != 0, s);

@@ -654,10 +654,37 @@ __global__ void head_sigmoid_gate_kernel(void* __restrict__ a, int dt, long a_st
     store_any(a, dt, at, load_any(a, dt, at) * (1.0f / (1.0f + expf(-z))));
 }
 
+// the same with 16 bytes per thread: eight bfloat16 or four float32 values of one head (dv a multiple of that many,
+// rows and the pointer aligned to 16 bytes)
+template <typename T>
+__global__ void head_sigmoid_gate_vec_kernel(T* __restrict__ a, long a_stride, const float* __restrict__ g, long g_stride,
+                                             int heads, int dv, long n_pieces) {
+    constexpr int V = 16 / sizeof(T);
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_pieces) return;
+    const int per_row = heads * dv / V;
+    const long t = idx / per_row;
+    const int c = (int)(idx % per_row) * V;
+    const float s = 1.0f / (1.0f + expf(-g[t * g_stride + c / dv]));
+    uint4* at = reinterpret_cast<uint4*>(a + (size_t)t * a_stride + c);
+    uint4 raw = *at;
+    T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = from_f32<T>(to_f32<T>(v[i]) * s);
+    *at = raw;
+}
+
 RS_EXPORT int rs_head_sigmoid_gate(void* a, int dt, long a_stride, const float* g, long g_stride, int heads, int dv,
                                    int n_tokens, void* stream) {
     const long n = (long)n_tokens * heads * dv;
     if (n <= 0) return 0;
+    const int v = dt == RS_F32 ? 4 : 8;
+    if ((dt == RS_F32 || dt == RS_BF16) && dv % v == 0 && a_stride % v == 0 && (uintptr_t)a % 16 == 0) {
+        const long pieces = n / v;
+        RS_DISPATCH_DTYPE(dt, T, (head_sigmoid_gate_vec_kernel<T><<<(unsigned)((pieces + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            reinterpret_cast<T*>(a), a_stride, g, g_stride, heads, dv, pieces)));
+        return rs_launch_result();
+    }
     head_sigmoid_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, dt, a_stride, g, g_stride, heads,
                                                                                            dv, n);
     return rs_launch_result();

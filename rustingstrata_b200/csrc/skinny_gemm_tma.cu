@@ -209,6 +209,7 @@ int launch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const Skin
         case EPI_STORE_F32: return launch<NT, EPI_STORE_F32>(mw, ma, p, max_ctas, defer, s);
         case EPI_ADD_F32: return launch<NT, EPI_ADD_F32>(mw, ma, p, max_ctas, defer, s);
         case EPI_SWIGLU_BF16: return launch<NT, EPI_SWIGLU_BF16>(mw, ma, p, max_ctas, defer, s);
+        case EPI_GEGLU_BF16: return launch<NT, EPI_GEGLU_BF16>(mw, ma, p, max_ctas, defer, s);
     }
     return (int)cudaErrorInvalidValue;
 }
@@ -231,7 +232,7 @@ RS_EXPORT int rs_skinny_gemm_bf16(const void* A, long lda, long a_rows, const vo
     if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((long)A & 15) || ((long)W & 15) || a_rows < M ||
         workspace == nullptr)
         return (int)cudaErrorInvalidValue;
-    if (epi == EPI_SWIGLU_BF16 && (N & 1)) return (int)cudaErrorInvalidValue;
+    if (RS_EPI_GATED(epi) && (N & 1)) return (int)cudaErrorInvalidValue;
     if (defer && (epi != EPI_ADD_F32 || M > 8)) return (int)cudaErrorInvalidValue;
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
     CUtensorMap mw, ma;

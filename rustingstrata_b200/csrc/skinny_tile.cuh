@@ -20,7 +20,7 @@ constexpr int CONSUMER_WARPS = 4;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
-enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_GEGLU_BF16 = 4 };
 
 struct SkinnyParams {
     void* C; long ldc;
@@ -42,7 +42,7 @@ __device__ __forceinline__ void store_tile(const SkinnyParams& p, const float (&
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const int m0 = 8 * j + 2 * t;
-        if (EPI == EPI_SWIGLU_BF16) {
+        if (RS_EPI_GATED(EPI)) {
             // rows of W alternate gate, up: lanes g and g ^ 1 hold a pair; the even one writes
             float partner[4];
 #pragma unroll
@@ -54,7 +54,7 @@ __device__ __forceinline__ void store_tile(const SkinnyParams& p, const float (&
                     const int m = m0 + (i & 1), n = (i >> 1) ? nb : na;
                     if (m < p.M && n + 1 < p.N) {
                         const float gate = acc[j][i], up = partner[i];
-                        out[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul_fast(gate, up));
+                        out[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(gated_mul_fast<EPI>(gate, up));
                     }
                 }
             }

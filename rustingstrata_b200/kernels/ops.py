@@ -377,7 +377,7 @@ def bf16lib():
     return _bf16
 
 
-EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
+EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_GEGLU_BF16 = 0, 1, 2, 3, 4
 
 
 def tensor_core_shape_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -390,11 +390,12 @@ def tensor_core_shape_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
             and weight.data_ptr() % 16 == 0)
 
 
-def _epilogue_code(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
+def _epilogue_code(out: torch.Tensor, accumulate: bool, swiglu) -> int:
+    """``swiglu``: False, or which gated epilogue: True or "silu" for SiLU(gate) * up, "gelu_tanh" for the tanh form of GELU."""
     if swiglu:
         if out.dtype != torch.bfloat16 or accumulate:
-            raise KernelError("the fused SiLU(gate)*up epilogue writes bfloat16 and does not accumulate")
-        return EPI_SWIGLU_BF16
+            raise KernelError("the fused act(gate)*up epilogue writes bfloat16 and does not accumulate")
+        return EPI_GEGLU_BF16 if swiglu == "gelu_tanh" else EPI_SWIGLU_BF16
     if out.dtype == torch.bfloat16:
         if accumulate:
             raise KernelError("accumulating products go into the float32 residual stream")
@@ -684,6 +685,8 @@ def reset_chain_barrier() -> None:
 def _chain_takes_product(a, weight, out, n_rows, swiglu: bool) -> bool:
     if _ACTIVE_CHAIN is None:            # asked first: the 32-bit engine must not load (or compile) the bfloat16 library
         return False
+    if swiglu == "gelu_tanh":            # the chained kernel has the SiLU gate only
+        return False
     lib = bf16lib()
     return (n_rows <= lib.rs_decode_chain_max_rows() and tensor_core_shape_ok(a, weight)
             and weight.numel() < SKINNY_MAX_WEIGHT and out.dtype in (torch.bfloat16, torch.float32)
@@ -715,18 +718,21 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_rows: int
 
 
 def linear_swiglu(a: torch.Tensor, weight_interleaved: torch.Tensor, out: torch.Tensor, n_rows: int,
-                  status: Optional[torch.Tensor] = None) -> None:
-    """out[:, j] = silu(a @ w[2j]) * (a @ w[2j+1]) in one kernel; only for shapes ``tensor_core_shape_ok`` takes."""
-    if _chain_takes_product(a, weight_interleaved, out, n_rows, True):
+                  status: Optional[torch.Tensor] = None, activation: str = "silu") -> None:
+    """out[:, j] = act(a @ w[2j]) * (a @ w[2j+1]) in one kernel, act SiLU or ("gelu_tanh") the tanh form of GELU; only for
+    shapes ``tensor_core_shape_ok`` takes."""
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"linear_swiglu: unknown activation '{activation}' (known: {', '.join(sorted(GATE_ACTIVATIONS))})")
+    if _chain_takes_product(a, weight_interleaved, out, n_rows, activation):
         _check_product(a, weight_interleaved, out, n_rows, True)
         _ACTIVE_CHAIN.add_product(a, weight_interleaved, out, n_rows, _epilogue_code(out, False, True))
         return
     if n_rows <= SKINNY_ROWS:
-        skinny_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
+        skinny_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=activation, status=status)
     elif n_rows <= MID_MAX_ROWS:
-        mid_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
+        mid_gemm_bf16(a, weight_interleaved, out, n_rows, swiglu=activation, status=status)
     else:
-        gemm_bf16_tc(a, weight_interleaved, out, n_rows, swiglu=True, status=status)
+        gemm_bf16_tc(a, weight_interleaved, out, n_rows, swiglu=activation, status=status)
 
 
 # ----------------------------------------------------------------------------- attention

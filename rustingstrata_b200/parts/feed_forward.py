@@ -46,8 +46,7 @@ class GatedMLP(FeedForward):
         # bfloat16 engine with 16-byte aligned rows: gate and up rows alternate, so the product's epilogue
         # applies SiLU(gate)*up to neighbouring accumulator columns and the [T, 2I] intermediate never
         # reaches memory.  Otherwise [gate; up] stacked, followed by the separate activation kernel.
-        self.fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0
-                      and self.activation == "silu")
+        self.fused = (g.dtype == torch.bfloat16 and self.runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0)
         if self.fused:
             self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden).contiguous()
         else:
@@ -60,7 +59,7 @@ class GatedMLP(FeedForward):
         gate_up = rt.get_scratch("gate_up")[:, : 2 * self.inter]
         act = rt.get_scratch("ff_act")[:, : self.inter]
         if self.fused:
-            ops.linear_swiglu(h, self.w_gate_up, act, T, status=ctx.status)
+            ops.linear_swiglu(h, self.w_gate_up, act, T, status=ctx.status, activation=self.activation)
         else:
             ops.linear(h, self.w_gate_up, gate_up, T)
             ops.silu_mul(gate_up, act, T, self.activation)

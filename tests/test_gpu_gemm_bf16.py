@@ -329,3 +329,21 @@ def test_skinny_and_tcgen05_agree_and_rows_do_not_depend_on_the_batch():
     one = torch.zeros(1, 2048, device=DEV)
     o.skinny_gemm_bf16(a[5:6].contiguous(), w, one, 1)
     assert torch.equal(one[0], g[5])                     # same k order whatever the batch
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (8, 1536, 320), (9, 768, 512), (64, 2048, 1024), (128, 520, 200), (129, 1280, 512),
+                                   (2048, 8192, 1024)])
+def test_gelu_gated_epilogue_in_every_product_kernel(M, N, K):
+    """out = gelu_tanh(a Wg.T) * (a Wu.T) on interleaved rows, through the engine's choice of kernel for the row count
+    (few rows, up to 128, tiled), against float64; and the SiLU gate beside it still gives SiLU."""
+    o = ops()
+    a, w = make(M, N, K, seed=3)
+    x = a.double() @ w.double().T
+    g, u = x[:, 0::2], x[:, 1::2]
+    gelu = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.zeros(M, N // 2, device=DEV, dtype=torch.bfloat16)
+    o.linear_swiglu(a, w, out, M, status=st, activation="gelu_tanh")
+    assert err(out, gelu * u) < 8e-3 and st.item() == 0
+    o.linear_swiglu(a, w, out, M, status=st)
+    assert err(out, g * torch.sigmoid(g) * u) < 8e-3 and st.item() == 0
