@@ -165,6 +165,17 @@ def _mlp(mlp: Any, w: str):
                      _require(shared, "ff", int, w + " shared") if shared is not None else None)
 
 
+def _same_tensors(a: KozasunLayerConfig, b: KozasunLayerConfig) -> bool:
+    """Whether two layers ask for tensors of the same names and shapes (constants such as a mask's size may differ)."""
+    def sizes(L):
+        m, f = L.mixer, L.mlp
+        mix = (L.type, m.heads, m.dim, m.vdim, getattr(m, "kv_heads", None), getattr(m, "kv_rank", None))
+        if f is None or isinstance(f, DenseConfig):
+            return mix + (None if f is None else ("dense", f.ff),)
+        return mix + (("moe", f.experts, f.expert_ff, f.shared_ff),)
+    return sizes(a) == sizes(b)
+
+
 @dataclass(frozen=True)
 class KozasunConfig:
     vocab: int
@@ -202,16 +213,20 @@ class KozasunConfig:
                 raise ConfigError(f"{w}: a layer is an object with 'type', 'mixer' and 'mlp'")
             src = L.get("weights_of")
             if src is not None:
-                if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(raw_layers) or src == i:
-                    raise ConfigError(f"{w}: 'weights_of' must name another layer, got {src!r}")
-                if not isinstance(raw_layers[src], Mapping) or raw_layers[src].get("weights_of") is not None:
-                    raise ConfigError(f"{w}: layer {src} has no tensors of its own to share")
+                # the layer whose tensors it runs; a layer that itself runs another's hands the question on
+                seen = {i}
+                while src is not None:
+                    if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(raw_layers) or src in seen:
+                        raise ConfigError(f"{w}: 'weights_of' must lead to another layer with tensors of its own, got {src!r}")
+                    seen.add(src)
+                    nxt = raw_layers[src].get("weights_of") if isinstance(raw_layers[src], Mapping) else None
+                    if nxt is None:
+                        break
+                    src = nxt
             layers.append(KozasunLayerConfig(L.get("type"), _mixer(L.get("type"), L["mixer"], w), _mlp(L.get("mlp"), w), src))
         for i, L in enumerate(layers):
-            if L.weights_of is not None:
-                o = layers[L.weights_of]
-                if (L.type, L.mixer, L.mlp) != (o.type, o.mixer, o.mlp):
-                    raise ConfigError(f"{where} layers[{i}]: a layer that uses layer {L.weights_of}'s tensors must equal it")
+            if L.weights_of is not None and not _same_tensors(L, layers[L.weights_of]):
+                raise ConfigError(f"{where} layers[{i}]: a layer that uses layer {L.weights_of}'s tensors needs its sizes")
         max_pos = d.get("max_positions", DEFAULT_MAX_POSITIONS)
         if isinstance(max_pos, bool) or not isinstance(max_pos, int) or max_pos <= 0:
             raise ConfigError(f"{where}: 'max_positions' must be a positive integer, got {max_pos!r}")

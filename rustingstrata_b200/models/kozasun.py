@@ -27,12 +27,17 @@ def build_kozasun_spec(cfg: KozasunConfig) -> ModelSpec:
     norm = lambda name, streams=1: PartSpec("layernorm", {"width": D, "eps": cfg.eps, "streams": streams},       # noqa: E731
                                             {"weight": name, "bias": name + ".b"})
     rope = lambda rot: PartSpec("rope_neox", {"n_rot": rot.dims, "base": rot.base, "base_bits": 64})             # noqa: E731
-    layers, order, index = [], [], {}
+    layers, index, order = [], {}, []
     for i, L in enumerate(cfg.layers):
-        if L.weights_of is not None:
-            order.append(LayerCall(index[L.weights_of]))
+        # tensors: the layer's own, or those of the layer it names.  An entry that equals the named layer's is one more
+        # call of that layer; one that differs in a constant (a mask's size, say) is a layer of its own on the same tensors.
+        owner = i if L.weights_of is None else L.weights_of
+        same = next((k for k, (o, other) in enumerate(index.get(owner, [])) if (other.type, other.mixer, other.mlp) ==
+                     (L.type, L.mixer, L.mlp)), None)
+        if same is not None:
+            order.append(LayerCall(index[owner][same][0]))
             continue
-        p = f"l{i}."
+        p = f"l{owner}."
         m = L.mixer
         parts = {"mixer_norm": norm(p + "norm1")}
         if L.type == ATTENTION:
@@ -80,9 +85,9 @@ def build_kozasun_spec(cfg: KozasunConfig) -> ModelSpec:
                     "expert": "gated_silu"}, t)
             if cfg.streams is not None:
                 block_tensors.update(ff_in=p + "hc2.in", ff_out=p + "hc2.out", ff_mix=p + "hc2.mix")
-        index[i] = len(layers)
+        index.setdefault(owner, []).append((len(layers), L))
+        order.append(LayerCall(len(layers)))
         layers.append(LayerSpec(PartSpec("hyper_connection", {"hidden": D, "streams": S}, block_tensors), parts))
-        order.append(LayerCall(index[i]))
     return ModelSpec(
         name="kozasun", vocab_size=cfg.vocab, hidden_size=D, max_positions=cfg.max_positions,
         embedding=PartSpec("table_sum", {"vocab": cfg.vocab, "width": D, "copies": S, "scale": cfg.embedding_scale,

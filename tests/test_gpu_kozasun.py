@@ -107,6 +107,9 @@ ONE_LAYER = {
     "shared_layer_runs_twice": M.config(97, 64, [(M.retention(2, 16, 16, (0.9, 0.99)), M.dense(48)), 0, (M.latent(2, 16, 16, 24, window=6), None), 2],
                                         streams=2),
 }
+# a layer that runs another layer's tensors with a window of its own
+ONE_LAYER["shared_layer_with_its_own_window"] = M.config(97, 64, [(M.latent(2, 16, 16, 24, window=6), M.dense(48)), 0], streams=2)
+ONE_LAYER["shared_layer_with_its_own_window"]["layers"][1]["mixer"]["mask"]["size"] = 11
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

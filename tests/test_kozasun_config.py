@@ -67,6 +67,20 @@ def test_a_layer_that_uses_another_layers_tensors_is_one_more_entry_of_the_run_o
     assert [c.layer for c in spec.order] == [0, 1, 2, 0, 3, 2] and all(c.cache is None for c in spec.order)
     names = set(manifest_for(cfg))
     assert not any(n.startswith(("l3.", "l5.")) for n in names) and any(n.startswith("l4.") for n in names)
+    # a layer may name a later layer, or one that itself names another: the tensors are those at the end of the chain
+    c = copy.deepcopy(cfg)
+    c["layers"] = [dict(c["layers"][2], weights_of=5), c["layers"][0], dict(c["layers"][2], weights_of=3), c["layers"][2],
+                   dict(c["layers"][0], weights_of=1), dict(c["layers"][2], weights_of=2)]
+    spec = arch.build_spec(arch.config_class.from_dict(c))
+    assert len(spec.layers) == 2 and [x.layer for x in spec.order] == [0, 1, 0, 0, 1, 0]
+    assert {n.split(".")[0] for n in manifest_for(c) if n.startswith("l")} == {"l1", "l3"}
+    # an entry that differs from the named layer's in a constant runs that layer's tensors with its own constant
+    c = copy.deepcopy(cfg)
+    c["layers"][5]["mixer"]["mask"]["size"] = 12
+    spec = arch.build_spec(arch.config_class.from_dict(c))
+    assert [x.layer for x in spec.order] == [0, 1, 2, 0, 3, 4] and spec.layers[4].parts["mixer"].params["window"] == 12
+    assert spec.layers[4].parts["mixer"].tensors == spec.layers[2].parts["mixer"].tensors
+    assert set(manifest_for(c)) == set(manifest_for(cfg))
 
 
 @pytest.mark.parametrize("bad", [
@@ -74,7 +88,8 @@ def test_a_layer_that_uses_another_layers_tensors_is_one_more_entry_of_the_run_o
     lambda c: c["layers"][0]["mixer"]["rot"].update(dims=9), lambda c: c["layers"][0]["mixer"].update(kv_heads=4),
     lambda c: c["layers"][1]["mixer"].update(decay=[0.5]), lambda c: c["layers"][0]["mlp"].update(kind="routed"),
     lambda c: c["layers"][1]["mlp"]["router"]["groups"].update(count=4), lambda c: c["layers"][1]["mlp"]["router"].update(top=5),
-    lambda c: c["layers"][3].update(weights_of=3), lambda c: c["layers"][3].update(weights_of=5),
+    lambda c: c["layers"][3].update(weights_of=3), lambda c: c["layers"][3].update(weights_of=6),
+    lambda c: (c["layers"][3].update(weights_of=5), c["layers"][5].update(weights_of=3)),
     lambda c: c["layers"][3]["mixer"].update(heads=3), lambda c: c["layers"][2]["mixer"].pop("kv_rank"),
     lambda c: c["layers"][2]["mixer"]["mask"].update(size=0)])
 def test_broken_configurations_are_refused_with_a_sentence(bad):

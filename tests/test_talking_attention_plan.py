@@ -6,9 +6,9 @@ from rustingstrata_b200.parts import talking_attention as TA
 from rustingstrata_b200.parts.base import HostBatch
 
 
-def make_part(mma_q=16, window=0):
+def make_part(mma_q=16, window=0, chunk=0):
     att = TA.TalkingAttention.__new__(TA.TalkingAttention)
-    att.q_per_cta, att.mma_q, att.window = 8, mma_q, window
+    att.q_per_cta, att.mma_q, att.window, att.chunk = 8, mma_q, window, chunk
     att.n_heads, att.n_kv, att.dk, att.dv = 16, 4, 64, 64
     return att
 
@@ -80,3 +80,13 @@ def test_rows_of_partial_sums_fit_the_workspace():
 def test_the_other_form_gets_plain_tiles():
     plan = make_part(mma_q=0).build_plan(batch([20, 1], [20, 90]))
     assert plan["work"].reshape(-1, 2).tolist() == [[1, 0], [0, 16], [0, 8], [0, 0]] and plan["qt"] == 8
+
+
+def test_blocks_of_positions_bound_the_keys_that_are_shared_out():
+    """With blocks of 1,024 positions a single token at position 3,999 walks the 928 keys of its block (29 key tiles), and
+    one at position 1,024 walks one key: the parts follow the block, not the sequence's length."""
+    plan = make_part(chunk=1024).build_plan(batch([1, 1], [4000, 1025]))
+    w = rows_of(plan)
+    by_seq = {s: w[w[:, 0] == s] for s in range(2)}
+    assert len(by_seq[0]) == by_seq[0][0, 3] == 29 // TA.MIN_PART_TILES
+    assert len(by_seq[1]) == 1 and by_seq[1][0, 3] == 1
