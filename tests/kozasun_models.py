@@ -91,18 +91,18 @@ CONFIGS = {
         0,
         (retention(2, 40, 12, (0.99, 0.5)), moe(5, 1, 24)),
         2,
-    ], eps=1e-6, streams=3, embedding_scale=0.5),
+    ], eps=1e-6, streams=3, embedding_scale=0.25),
     # no streams (the plain residual sum), no embedding scale, no masks, no rotation in the attention, one kv head,
     # one group kept of two, a width the tensor-core products refuse
     "Q": config(130, 100, [
-        (attention(5, 1, 32, 8), moe(8, 3, 24, scale=2.0, groups=(2, 1), shared=40)),
+        (attention(5, 1, 32, 8), moe(10, 3, 24, scale=1.75, groups=(2, 1), shared=40)),
         (latent(2, 24, 8, 20), dense(56)),
         (retention(1, 64, 32, (0.98,), rot=(16, 1e4)), None),
     ], eps=1e-5),
     # wider, two streams, heads of the sizes the tensor-core kernels take, for long sequences
     "R": config(320, 256, [
-        (attention(4, 2, 64, 64, rot=(32, 1e5), chunk=128), dense(384)),
-        (retention(4, 32, 64, (0.97, 0.99, 0.995, 0.999), rot=(32, 1e6)), moe(8, 2, 64, scale=2.5, groups=(4, 2), shared=128)),
+        (attention(4, 2, 64, 64, rot=(32, 1e5), chunk=128), dense(320)),
+        (retention(4, 64, 32, (0.97, 0.99, 0.995, 0.999), rot=(32, 5e5)), moe(12, 2, 64, scale=2.5, groups=(4, 2), shared=128)),
         (latent(4, 48, 32, 80, window=200), dense(256)),
         1,
     ], eps=1e-5, streams=2, embedding_scale=2.0),

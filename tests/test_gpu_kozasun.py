@@ -101,7 +101,7 @@ ONE_LAYER = {
     "latent_rank_that_needs_padding": M.config(97, 64, [(M.latent(4, 8, 16, 21, window=16), None)], streams=2),
     "dense_feed_forward": M.config(97, 64, [(M.retention(1, 8, 8, (0.9,)), M.dense(120))], streams=2, embedding_scale=3.0),
     "experts_in_groups": M.config(97, 64, [(M.retention(1, 8, 8, (0.9,)), M.moe(12, 3, 24, scale=2.0, groups=(4, 2), shared=40))], streams=2),
-    "experts_one_group_kept": M.config(97, 64, [(M.retention(1, 8, 8, (0.9,)), M.moe(8, 3, 16, scale=0.7, groups=(2, 1), shared=8))]),
+    "experts_one_group_kept": M.config(97, 64, [(M.retention(1, 8, 8, (0.9,)), M.moe(10, 4, 16, scale=0.7, groups=(2, 1), shared=8))]),
     "experts_all_groups_kept": M.config(97, 64, [(M.retention(1, 8, 8, (0.9,)), M.moe(6, 2, 16, groups=(3, 3)))], streams=2),
     "experts_top_one_no_groups_no_shared": M.config(97, 64, [(M.retention(1, 8, 8, (0.9,)), M.moe(5, 1, 32, scale=1.0))], streams=4),
     "shared_layer_runs_twice": M.config(97, 64, [(M.retention(2, 16, 16, (0.9, 0.99)), M.dense(48)), 0, (M.latent(2, 16, 16, 24, window=6), None), 2],

@@ -25,9 +25,9 @@ def test_architecture_is_found_by_its_key_and_sizes_come_from_the_file():
     cfg = M.CONFIGS["P"]
     arch = resolve_architecture(cfg)
     c = arch.config_class.from_dict(cfg)
-    assert isinstance(c, KozasunConfig) and (c.vocab, c.width, c.eps, c.streams, c.embedding_scale) == (211, 96, 1e-6, 3, 0.5)
+    assert isinstance(c, KozasunConfig) and (c.vocab, c.width, c.eps, c.streams, c.embedding_scale) == (211, 96, 1e-6, 3, 0.25)
     spec = arch.build_spec(c)
-    assert spec.n_streams == 3 and spec.embedding.params["scale"] == 0.5 and spec.embedding.params["copies"] == 3
+    assert spec.n_streams == 3 and spec.embedding.params["scale"] == 0.25 and spec.embedding.params["copies"] == 3
     a = spec.layers[0].parts["mixer"].params
     assert (a["n_heads"], a["n_kv_heads"], a["dim"], a["vdim"], a["scale"], a["eps"], a["chunk"], a["window"]) == \
         (6, 2, 24, 40, 0.3, 1e-6, 20, None)
