@@ -10,7 +10,9 @@
 //   1. S = Q K^T: warp w computes the 16 x 8 block of keys 8w .. 8w + 7 over the whole row width, scales and masks it
 //      (causal, window, the split's range) and leaves it in shared memory;
 //   2. online softmax in float32: 16 threads per row take the tile's maximum, the probabilities (rounded to bfloat16
-//      for the product), the running sum and the factor by which the row's earlier results shrink;
+//      for the product; with split_p in two bfloat16 terms, p = hi + lo with |lo| <= 2^-9 p, both of which are multiplied,
+//      so that the product carries the float32 weight), the running sum and the factor by which the row's earlier
+//      results shrink;
 //   3. O += P V with V the same key rows: warp w owns a slice of the row's coordinates (an eighth, rounded up to 8).
 // Key tiles start at multiples of 64 from key 0 and the split form's splits at multiples of the split size, so the order
 // in which a query's keys are reduced depends on its position alone.  The split form leaves un-normalised partial
@@ -37,6 +39,7 @@ struct LatParams {
     const int* split_start; float* partial; int partial_slots;
     int* status;
     int n_buf;                                      // key buffers in shared memory: 2 (tile i + 1 loads under tile i) or 1
+    int split_p;                                    // 1: the softmax weights enter P V in two bfloat16 terms
 };
 
 __device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
@@ -56,7 +59,8 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
     __nv_bfloat16* Ks = Qs + ROWS * pitch;                                          // [n_buf][KT][pitch]
     float* Ss = reinterpret_cast<float*>(Ks + p.n_buf * KT * pitch);                      // [ROWS][S_PITCH]
     __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + ROWS * S_PITCH);      // [ROWS][P_PITCH]
-    float* stat_m = reinterpret_cast<float*>(Ps + ROWS * P_PITCH);                  // [ROWS] each
+    __nv_bfloat16* Pl = Ps + ROWS * P_PITCH;                                        // [ROWS][P_PITCH] the weights' second terms
+    float* stat_m = reinterpret_cast<float*>(Pl + ROWS * P_PITCH);                  // [ROWS] each
     float* stat_l = stat_m + ROWS;
     float* stat_c = stat_l + ROWS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -204,6 +208,14 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
             uint2 pk;
             pk.x = pack_bf16(p0, p1); pk.y = pack_bf16(p2, p3);
             *reinterpret_cast<uint2*>(Ps + r * P_PITCH + j * 4) = pk;
+            if (p.split_p) {
+                const __nv_bfloat162 h01 = *reinterpret_cast<const __nv_bfloat162*>(&pk.x);
+                const __nv_bfloat162 h23 = *reinterpret_cast<const __nv_bfloat162*>(&pk.y);
+                uint2 lo;
+                lo.x = pack_bf16(p0 - __low2float(h01), p1 - __high2float(h01));
+                lo.y = pack_bf16(p2 - __low2float(h23), p3 - __high2float(h23));
+                *reinterpret_cast<uint2*>(Pl + r * P_PITCH + j * 4) = lo;
+            }
             if (j == 0) { stat_m[r] = m_new; stat_l[r] = stat_l[r] * corr + sum; stat_c[r] = corr; }
         }
         __syncthreads();
@@ -213,17 +225,20 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const LatP
 #pragma unroll
             for (int n = 0; n < NT_MAX; ++n) { acc[n][0] *= c0; acc[n][1] *= c0; acc[n][2] *= c1; acc[n][3] *= c1; }
             const uint32_t pa = smem_addr(Ps + a_row * P_PITCH + a_col);
+            const uint32_t pl = smem_addr(Pl + a_row * P_PITCH + a_col);
             const uint32_t vb = smem_addr(Kt + (lane & 15) * pitch + dim_lo);
 #pragma unroll
             for (int kk = 0; kk < KT; kk += 16) {
-                uint32_t a[4];
+                uint32_t a[4], al[4] = {0u, 0u, 0u, 0u};
                 ldmatrix_x4(pa + kk * 2, a[0], a[1], a[2], a[3]);
+                if (p.split_p) ldmatrix_x4(pl + kk * 2, al[0], al[1], al[2], al[3]);
 #pragma unroll
                 for (int n = 0; n < NT_MAX; ++n) {
                     if (n < my_nt) {
                         uint32_t b0, b1;
                         ldmatrix_x2_trans(vb + (kk * pitch + n * 8) * 2, b0, b1);
                         mma16816(acc[n], a, b0, b1);
+                        if (p.split_p) mma16816(acc[n], al, b0, b1);
                     }
                 }
             }
@@ -316,7 +331,7 @@ __global__ void latent_merge_kernel(const LatParams p) {
 
 size_t latent_smem_bytes(int lat, int n_buf) {
     const int pitch = lat + 8;
-    return (size_t)(ROWS + n_buf * KT) * pitch * 2 + (size_t)ROWS * S_PITCH * 4 + (size_t)ROWS * P_PITCH * 2 + 3 * ROWS * 4;
+    return (size_t)(ROWS + n_buf * KT) * pitch * 2 + (size_t)ROWS * S_PITCH * 4 + 2 * (size_t)ROWS * P_PITCH * 2 + 3 * ROWS * 4;
 }
 
 // Two CTAs on an SM hide more than a second key buffer does: where two buffers would leave room for one CTA only
@@ -343,7 +358,7 @@ RS_EXPORT int rs_attention_latent_bf16(const void* q, long q_stride, void* out, 
                                        int table_stride, const int* q_start, const int* kv_len, const int* work, int n_work,
                                        int n_heads, int lat, int window, float scale, int decode, int split_keys,
                                        int max_splits, const int* split_start, float* partial, int partial_slots,
-                                       int* status, void* stream) {
+                                       int split_p, int* status, void* stream) {
     if (n_work <= 0) return 0;
     if (!rs_attention_latent_supported(n_heads, lat, page_size) || q_stride % 8 || out_stride % 2 || page_stride % 8 ||
         ((size_t)q & 15) || ((size_t)cache & 15) || ((size_t)out & 3))
@@ -358,6 +373,7 @@ RS_EXPORT int rs_attention_latent_bf16(const void* q, long q_stride, void* out, 
     p.n_heads = n_heads; p.lat = lat; p.hc = heads_per_cta(n_heads, decode); p.tok_per_cta = decode ? 1 : ROWS / p.hc;
     p.window = window; p.scale = scale; p.decode = decode; p.split_keys = split_keys; p.max_splits = max_splits;
     p.split_start = split_start; p.partial = partial; p.partial_slots = partial_slots; p.status = status;
+    p.split_p = split_p ? 1 : 0;
     p.n_buf = latent_smem_bytes(lat, 2) <= HALF_SM_SMEM ? 2 : 1;
     const size_t smem = latent_smem_bytes(lat, p.n_buf);
     static std::atomic<size_t> smem_allowed[64];

@@ -370,7 +370,7 @@ def bf16lib():
         lib.rs_attention_latent_q_per_cta.argtypes = [c_int]
         lib.rs_attention_latent_bf16.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_void_p,
                                                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                                                 c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+                                                 c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.rs_attention_prefill_bf16_supported.argtypes = [c_int, c_int, c_int]
         lib.rs_attention_prefill_bf16_q_per_cta.argtypes = [c_int, c_int]
         _bf16 = lib
@@ -966,11 +966,12 @@ def attention_latent(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      q_start: torch.Tensor, kv_len: torch.Tensor, work: torch.Tensor, n_work: int, n_heads: int, lat: int,
                      page_size: int, window: int, scale: float, decode: bool, status: torch.Tensor, split_keys: int = 128,
                      max_splits: int = 1, split_start: Optional[torch.Tensor] = None, total_splits: int = 0,
-                     partial: Optional[torch.Tensor] = None) -> None:
+                     partial: Optional[torch.Tensor] = None, split_weights: bool = False) -> None:
     """Attention of ``n_heads`` query heads over a one-plane cache [pages, 1, 1, page_size, lat] whose rows are key and
     value at once, on the tensor cores (csrc/attention_latent_mma.cu).  ``work``: (sequence, first query) tiles of
     :func:`attention_latent_q_per_cta` tokens, or with ``decode`` one sequence per entry, the keys cut into splits whose
-    partial results (layout of :func:`attention_simt`) are merged by a second kernel."""
+    partial results (layout of :func:`attention_simt`) are merged by a second kernel.  ``split_weights``: the softmax weights
+    enter the weighted sum in two bfloat16 terms (the float32 weight to 2^-17) instead of rounded to bfloat16."""
     _cuda(q, out, cache, block_table, q_start, kv_len, work, status, partial, split_start)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
@@ -991,8 +992,8 @@ def attention_latent(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
     _check(bf16lib().rs_attention_latent_bf16(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], page_size,
         _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(work), n_work, n_heads, lat, int(window),
-        float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start), _ptr(partial), slots, _ptr(status),
-        _stream()), "attention_latent", 2 if decode else 1)
+        float(scale), 1 if decode else 0, split_keys, max_splits, _ptr(split_start), _ptr(partial), slots,
+        1 if split_weights else 0, _ptr(status), _stream()), "attention_latent", 2 if decode else 1)
 
 
 def attention_decode_items(split_start: torch.Tensor, n_work: int, n_kv: int, max_splits: int, items: torch.Tensor) -> None:

@@ -59,7 +59,7 @@ def build_kozasun_spec(cfg: KozasunConfig) -> ModelSpec:
         elif L.type == LATENT_ATTENTION:
             parts["mixer"] = PartSpec("latent_attention", {
                 "hidden": D, "n_heads": m.heads, "dim": m.dim, "rot_dim": 0, "vdim": m.vdim, "kv_rank": m.kv_rank,
-                "scale": m.scale, "eps": cfg.eps, "window": m.window, "gate": True}, {
+                "scale": m.scale, "eps": cfg.eps, "window": m.window, "gate": True, "weights_bits": 32}, {
                 "q_proj": p + "mix.q", "dkv_proj": p + "mix.dkv", "latent_norm": p + "mix.dkv.norm", "uk_proj": p + "mix.uk",
                 "uv_proj": p + "mix.uv", "g_proj": p + "mix.g", "o_proj": p + "mix.o"})
         else:

@@ -32,7 +32,8 @@ from .spec import CacheNeed, PartSpec, TensorNeed
 @register_part("mixer", "latent_attention")
 class LatentAttention(PagedAttention):
     """params: hidden, n_heads, dim (unrotated query/key size per head), rot_dim, vdim, kv_rank, scale, eps (of the
-    latent's norm), window (None: every key), gate (bool, default False).  tensors: q_proj, dkv_proj, latent_norm, uk_proj
+    latent's norm), window (None: every key), gate (bool, default False), weights_bits (16, the default: the tensor-core
+    kernel rounds the softmax weights to bfloat16 for the weighted sum; 32: it multiplies them in two bfloat16 terms).  tensors: q_proj, dkv_proj, latent_norm, uk_proj
     [heads * dim, kv_rank], uv_proj [heads * vdim, kv_rank], o_proj, and g_proj [heads, hidden] with a gate.  The layer's position part rotates the first ``n_rot`` <= rot_dim coordinates of the rotated
     parts (pairs (2i, 2i + 1): a part whose ``pairing`` is "interleaved")."""
     chain_safe = False
@@ -55,6 +56,7 @@ class LatentAttention(PagedAttention):
         self._tensor_cores = None
         self.latent_eps = float(p["eps"])
         self.has_gate = bool(p.get("gate", False))
+        self.split_weights = int(p.get("weights_bits", 16)) == 32
         self.dkv_cols = self.rank + self.rot_dim + (self.n_heads if self.has_gate else 0)
         if position is not None and getattr(position, "cos_sin", None) is not None:
             if getattr(position, "pairing", "") != "interleaved":
@@ -116,7 +118,7 @@ class LatentAttention(PagedAttention):
         plan = ctx.plans[self.plan_key()]
         common = dict(q=q, out=out, cache=call.cache, block_table=ctx.block_tables[call.cache_group], q_start=ctx.q_start,
                       kv_len=ctx.kv_len, n_heads=self.n_heads, lat=self.lat, page_size=rt.page_size, window=self.window,
-                      scale=self.scale, status=ctx.status)
+                      scale=self.scale, status=ctx.status, split_weights=self.split_weights)
         if plan["n_prefill"]:
             ops.attention_latent(work=plan["prefill_work"], n_work=plan["n_prefill"], decode=False, **common)
         if plan["n_decode"]:

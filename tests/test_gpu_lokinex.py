@@ -403,11 +403,12 @@ def test_kernels_of_the_new_parts_against_torch():
     assert torch.allclose(state[0].cpu().reshape(taps - 1, C), xin[8:11], atol=0)
 
 
+@pytest.mark.parametrize("split_weights", [False, True])
 @pytest.mark.parametrize("heads,lat,page", [(7, 96, 16), (16, 576, 16), (3, 48, 8), (20, 128, 32), (1, 16, 4)])
-def test_tensor_core_latent_attention_against_torch(heads, lat, page):
+def test_tensor_core_latent_attention_against_torch(heads, lat, page, split_weights):
     """The tensor-core kernel of latent attention (portions and the split form) against a plain float32 computation on
     the same bfloat16 inputs: sequences of unequal length, portions that start in the middle of a page, single tokens
-    beside them, with and without a window."""
+    beside them, with and without a window; the softmax weights rounded to bfloat16 or in two bfloat16 terms."""
     from rustingstrata_b200.kernels import ops
     dev = torch.device("cuda:0")
     g = torch.Generator(device="cpu").manual_seed(heads * 1000 + lat)
@@ -449,7 +450,7 @@ def test_tensor_core_latent_attention_against_torch(heads, lat, page):
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         common = dict(q=q.to(dev), out=out, cache=cache.to(dev), block_table=table.to(dev), q_start=q_start.to(dev),
                       kv_len=torch.tensor(kv_lens, dtype=torch.int32, device=dev), n_heads=heads, lat=lat, page_size=page,
-                      window=window, scale=scale, status=status)
+                      window=window, scale=scale, status=status, split_weights=split_weights)
         ops.attention_latent(work=torch.tensor(pre, dtype=torch.int32, device=dev).reshape(-1), n_work=len(pre), decode=False, **common)
         ops.attention_latent(work=torch.tensor(dec, dtype=torch.int32, device=dev), n_work=len(dec), decode=True, split_keys=128,
                              max_splits=max(splits), split_start=split_start, total_splits=sum(splits), partial=partial, **common)

@@ -38,7 +38,7 @@ def test_architecture_is_found_by_its_key_and_sizes_come_from_the_file():
     assert spec.layers[1].parts["mixer_position"].params["n_rot"] == 24
     la = spec.layers[2].parts["mixer"].params
     assert (la["n_heads"], la["dim"], la["vdim"], la["kv_rank"], la["rot_dim"], la["window"], la["scale"], la["gate"]) == \
-        (3, 16, 24, 40, 0, 33, 0.25, True)
+        (3, 16, 24, 40, 0, 33, 0.25, True) and la["weights_bits"] == 32
     assert "feed_forward" not in spec.layers[2].parts and "mixer_position" not in spec.layers[2].parts
     assert spec.layers[0].parts["feed_forward"].params == {"hidden": 96, "intermediate": 160, "activation": "gelu_tanh"}
     m = spec.layers[1].parts["feed_forward"].params
