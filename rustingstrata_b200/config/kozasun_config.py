@@ -3,7 +3,7 @@
     architecture: "Kozasun"; vocab; width; norm: {eps}; embedding: {scale} (absent: 1); streams (absent: one stream with
     the plain residual sum); max_positions (optional);
     layers: [{type: "attention" | "retention" | "latent_attention", mixer: {...}, mlp: null | {...}, weights_of: j}, ...]
-    attention mixer:        heads, kv_heads (absent: heads), dim, vdim (absent: dim), scale, rot: null | {base, dims},
+    attention mixer:        heads, kv_heads (absent: heads), dim, vdim (absent: dim), scale (absent: dim^-1/2), rot: null | {base, dims},
                             mask: null | {size} (keys of the query's own block of ``size`` positions)
     retention mixer:        heads, dim, vdim (absent: dim), decay: [one number per head], rot: null | {base, dims}
     latent_attention mixer: heads, dim, vdim (absent: dim), kv_rank, scale, mask: null | {size} (the last ``size`` keys)
@@ -113,11 +113,16 @@ def _optional_int(m: Mapping[str, Any], key: str, default: int, w: str) -> int:
     return _require(m, key, int, w) if m.get(key) is not None else default
 
 
+def _scale(m: Mapping[str, Any], dim: int, w: str) -> float:
+    """The score scale; a file that names none gets dim^-1/2."""
+    return _require(m, "scale", float, w) if m.get("scale") is not None else float(dim) ** -0.5
+
+
 def _mixer(kind: str, m: Mapping[str, Any], w: str):
     heads, dim = _require(m, "heads", int, w), _require(m, "dim", int, w)
     vdim = _optional_int(m, "vdim", dim, w)
     if kind == ATTENTION:
-        mixer = AttentionMixerConfig(heads, _optional_int(m, "kv_heads", heads, w), dim, vdim, _require(m, "scale", float, w),
+        mixer = AttentionMixerConfig(heads, _optional_int(m, "kv_heads", heads, w), dim, vdim, _scale(m, dim, w),
                                      _rotation(m, dim, w), _mask(m, w))
         if mixer.heads % mixer.kv_heads:
             raise ConfigError(f"{w}: {mixer.heads} heads are not a multiple of {mixer.kv_heads} kv_heads")
@@ -129,7 +134,7 @@ def _mixer(kind: str, m: Mapping[str, Any], w: str):
             raise ConfigError(f"{w}: 'decay' must list one number per head ({heads})")
         return RetentionMixerConfig(heads, dim, vdim, tuple(float(d) for d in decay), _rotation(m, dim, w))
     if kind == LATENT_ATTENTION:
-        return LatentMixerConfig(heads, dim, vdim, _require(m, "kv_rank", int, w), _require(m, "scale", float, w), _mask(m, w))
+        return LatentMixerConfig(heads, dim, vdim, _require(m, "kv_rank", int, w), _scale(m, dim, w), _mask(m, w))
     raise ConfigError(f"{w}: unknown layer type {kind!r} (known: {ATTENTION}, {RETENTION}, {LATENT_ATTENTION})")
 
 
